@@ -1,0 +1,108 @@
+/* C ABI of libnsa_b200.so: the B200 (sm_100a) kernels of the Native Sparse Attention path.
+ *
+ * The reference project has no native boundary of its own: its boundary is the Python API of the `nsa`
+ * package, whose autograd functions launch Triton kernels.  Each entry point below names the reference
+ * interface (file:line in the reference project) whose kernels it replaces; the Python package
+ * `nsa_b200` keeps the reference's module/function signatures and calls these through ctypes.
+ *
+ * Conventions
+ *  - Every pointer is a device pointer owned by the caller (inputs, outputs and workspaces alike).  The
+ *    library never allocates or frees device memory and keeps no pointer after a call returns.
+ *  - Tensors are contiguous, bf16 unless stated, with the layouts given per function; `void* stream` is a
+ *    cudaStream_t.  Work is enqueued on that stream; no entry point synchronises except
+ *    nsa_device_status().
+ *  - Return value: 0 on success; negative = rejected arguments / unsupported configuration (text in
+ *    nsa_last_error(), thread local); positive = cudaError_t from a launch.
+ *  - Supported: head_dim D in {64, 128}; query heads per KV head a multiple of 16; selection block size
+ *    in {16, 32, 64}.
+ *  - Kernels bound every internal wait; if one gives up it records a code that nsa_device_status()
+ *    returns (0 = healthy).
+ */
+#ifndef NSA_B200_H_
+#define NSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int nsa_abi_version(void);
+const char* nsa_last_error(void);
+/* Synchronises the current device, returns and clears the device-side error code (0 = none). */
+int nsa_device_status(void);
+
+/* ---- compression -------------------------------------------------------------------------------
+ * Replaces compress_kv / _compress_kv.forward (nsa/compression_kv.py:178-217, kernel :21-57) and the two
+ * nn.Conv1d calls of KVCompressor.forward (nsa/compression_kv.py:301-307).
+ * x [tok,H,D]; w [block*D, D] (row j*D+c multiplies channel c of in-block offset j; a Conv1d weight
+ * [D,D,block] is passed as weight.permute(2,1,0)); bias [D] or NULL; y [out_tok,H,D];
+ * cu_in / cu_out: device int32 [nseq+1] cumulative input / output lengths; max_out = longest output. */
+int nsa_compress_fwd(const void* x, const void* w, const void* bias, void* y, const int32_t* cu_in,
+                     const int32_t* cu_out, int nseq, int H, int D, int block, int stride, int max_out,
+                     void* stream);
+/* Replaces _compress_kv.backward (nsa/compression_kv.py:219-266, kernels :62-171) and the Conv1d backward.
+ * dy [out_tok,H,D] -> dx [tok,H,D] bf16 (NULL to skip), dw [block*D, D] fp32 (NULL to skip),
+ * dbias [D] fp32 (NULL to skip).  ws: nsa_compress_bwd_workspace_bytes() bytes, needed when dw != NULL. */
+int nsa_compress_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, float* dbias, void* ws,
+                     size_t ws_bytes, const int32_t* cu_in, const int32_t* cu_out, int nseq, int H, int D,
+                     int block, int stride, int max_in, int total_out, void* stream);
+size_t nsa_compress_bwd_workspace_bytes(int nseq, int H, int D, int block);
+
+/* ---- compressed attention + block selection ------------------------------------------------------
+ * Replaces _attention.forward (nsa/triton_attention.py:421-476: _attn_fwd, softmax_kernel, group sum,
+ * avg_pool1d, topk) with one kernel; the [B,Hq,T,Tc] score tensor is never materialised.
+ * q [B,T,Hq,D]; ck,cv [B,Tc,Hk,D] (Hq/Hk a multiple of 16); o [B,T,Hq,D]; lse [B,T,Hq] fp32 (natural log,
+ * -inf for rows that see nothing).  If n_sel > 0: sel_idx [B,T,Hq/16,n_sel] int32 receives the top-n
+ * pooled blocks (ties to the lower index, -1 when fewer than n_sel blocks exist) and sel_scores (NULL or
+ * [B,Hq/16,T,n_pool] fp32) the pooled scores; n_pool = nsa_pool_out_len(Tc, pool_k, pool_s, pool_p). */
+int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
+                     float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride,
+                     int causal, float scale, int n_sel, int pool_k, int pool_s, int pool_p, void* stream);
+int nsa_pool_out_len(int n, int pool_k, int pool_s, int pool_p);
+/* Replaces _attention.backward (nsa/triton_attention.py:479-546).  dout [B,T,Hq,D]; delta [B,T,Hq] fp32 =
+ * rowsum(o*dout) (times gate if gate != NULL); gate [B,T,Hq] or NULL scales dout per row.
+ * dq [B,T,Hq,D] (added to when accumulate_dq); dck,dcv [B,Tc,Hk,D]. */
+int nsa_cmp_attn_bwd(const void* q, const void* ck, const void* cv, const float* lse, const void* dout,
+                     const float* delta, const void* gate, void* dq, int accumulate_dq, void* dck, void* dcv,
+                     void* ws, size_t ws_bytes, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride,
+                     int causal, float scale, void* stream);
+size_t nsa_cmp_attn_bwd_workspace_bytes(int B, int T, int Tc, int Hk, int D);
+
+/* ---- selected-block + sliding-window attention ----------------------------------------------------
+ * Replaces ParallelNSAFunction.forward / parallel_nsa_fwd (nsa/selection_attn.py:90-148, kernel :401-517)
+ * and the gated sums of parallel_nsa (:808-811) and NSAAttention.forward (nsa/nsa.py:133).
+ * q [B,T,Hq,D]; k,v [B,T,Hkv,D]; idx [B,T,Hkv,S] int32 (idx64 = 0) or int64 (idx64 = 1); counts [B,T,Hkv]
+ * int32 or NULL.  Outputs o_slc, lse_slc, and when window > 0 o_swa, lse_swa.  If o != NULL also writes
+ * o = g_slc*o_slc + g_swa*o_swa + g_cmp*o_cmp (a NULL tensor drops its term; a NULL gate means 1). */
+int nsa_sel_swa_fwd(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                    void* o_slc, float* lse_slc, void* o_swa, float* lse_swa, const void* g_slc, const void* g_swa,
+                    const void* o_cmp, const void* g_cmp, void* o, int B, int T, int Hq, int Hkv, int D, int S, int BS,
+                    int window, float scale, void* stream);
+/* Replaces ParallelNSAFunction.backward / parallel_nsa_bwd (nsa/selection_attn.py:572-676: preprocess, dq,
+ * block mask and dkv kernels).  The dense block mask is replaced by a reverse index built in ws.
+ * Per branch: dout, lse, delta (fp32, = rowsum(o*dout) times gate if given), gate (or NULL).  The window
+ * branch is skipped when window == 0.  dq [B,T,Hq,D] (added to when accumulate_dq); dk,dv [B,T,Hkv,D]. */
+int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                    const void* dout_slc, const float* lse_slc, const float* delta_slc, const void* gate_slc,
+                    const void* dout_swa, const float* lse_swa, const float* delta_swa, const void* gate_swa, void* dq,
+                    int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
+                    int D, int S, int BS, int window, float scale, void* stream);
+size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS);
+
+/* ---- helpers --------------------------------------------------------------------------------------
+ * delta[r] = (gate ? gate[r] : 1) * sum_d o[r,d]*dout[r,d] (fp32, NULL to skip) and
+ * dgate[r] = sum_d o[r,d]*dout[r,d] (bf16, NULL to skip); rows = B*T*Hq.
+ * Replaces parallel_nsa_bwd_kernel_preprocess (nsa/selection_attn.py:520-530), _attn_bwd_preprocess
+ * (nsa/triton_attention.py:184-199) and the gate gradients of the addcmul at nsa/nsa.py:133. */
+int nsa_rowdot(const void* o, const void* dout, const void* gate, float* delta, void* dgate, long long rows, int D,
+               void* stream);
+/* o = g0*a0 + g1*a1 + g2*a2 (NULL tensor: term dropped; NULL gate: 1).  nsa/nsa.py:133. */
+int nsa_combine(const void* a0, const void* g0, const void* a1, const void* g1, const void* a2, const void* g2,
+                void* o, long long rows, int D, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NSA_B200_H_ */

@@ -1,0 +1,320 @@
+// The C ABI of libnsa_b200.so (declared in include/nsa_b200.h): argument checks, workspace carving and kernel
+// launches.  No torch types, no allocation, no synchronisation except nsa_device_status().
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "../../include/nsa_b200.h"
+#include "kernels.h"
+#include "tmap.h"
+
+namespace nsa {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int check_attn_shape(const char* who, int B, int T, int Hq, int Hk, int D) {
+  if (B <= 0 || T <= 0 || Hq <= 0 || Hk <= 0) return fail(-1, "%s: empty or negative shape", who);
+  if (D != 64 && D != 128) return fail(-2, "%s: head_dim %d not supported (64 or 128)", who, D);
+  if (Hq % Hk != 0 || (Hq / Hk) % 16 != 0)
+    return fail(-3, "%s: query heads per KV head must be a multiple of 16 (Hq=%d, Hkv=%d)", who, Hq, Hk);
+  return 0;
+}
+
+static int cmp_segments(int T, int* seg_len) {
+  int nseg = (T + 1023) / 1024;
+  if (nseg > 16) nseg = 16;
+  if (nseg < 1) nseg = 1;
+  int sl = (T + nseg - 1) / nseg;
+  sl = (sl + 63) / 64 * 64;
+  *seg_len = sl;
+  return (T + sl - 1) / sl;
+}
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" {
+
+int nsa_abi_version(void) { return 1; }
+
+const char* nsa_last_error(void) { return g_err; }
+
+int nsa_device_status(void) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail(1000 + (int)e, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+  int worst = 0, v = 0;
+  int (*fns[])(int*) = {sel_status, dense_status, kv_status, compress_status, misc_status};
+  for (auto f : fns) {
+    v = 0;
+    const int rc = f(&v);
+    if (rc) return fail(1000 + rc, "reading the device status failed: %s", cudaGetErrorString((cudaError_t)rc));
+    if (v && !worst) worst = v;
+  }
+  if (worst) fail(worst, "a kernel gave up waiting on its pipeline (code %d)", worst);
+  return worst;
+}
+
+int nsa_pool_out_len(int n, int k, int s, int p) {
+  if (n <= 0 || k <= 0 || s <= 0) return 0;
+  const int num = n + 2 * p - k;
+  int out = (num >= 0 ? (num + s - 1) / s : -((-num) / s)) + 1;
+  if ((out - 1) * s >= n + p) --out;
+  return out < 0 ? 0 : out;
+}
+
+// ---- compression ------------------------------------------------------------------------------------
+int nsa_compress_fwd(const void* x, const void* w, const void* bias, void* y, const int32_t* cu_in,
+                     const int32_t* cu_out, int nseq, int H, int D, int block, int stride, int max_out,
+                     void* stream) {
+  if (!x || !w || !y || !cu_in || !cu_out) return fail(-1, "nsa_compress_fwd: null pointer");
+  if (nseq <= 0 || H <= 0) return fail(-1, "nsa_compress_fwd: empty shape");
+  if (stride <= 0 || block <= 0 || block % stride) return fail(-4, "nsa_compress_fwd: block must be a multiple of stride");
+  if (!aligned16(x) || !aligned16(w) || !aligned16(y)) return fail(-5, "nsa_compress_fwd: pointers must be 16-byte aligned");
+  CompressArgs a = {};
+  a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = (const bf16*)bias; a.y = (bf16*)y;
+  a.cu_in = cu_in; a.cu_out = cu_out; a.nseq = nseq; a.H = H; a.D = D; a.l = block; a.d = stride; a.max_out = max_out;
+  return launch_compress_fwd(a, (cudaStream_t)stream);
+}
+
+size_t nsa_compress_bwd_workspace_bytes(int nseq, int H, int D, int block) {
+  long long split = (long long)nseq * H;
+  if (split > 32) split = 32;
+  return (size_t)split * block * D * D * sizeof(float);
+}
+
+int nsa_compress_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, float* dbias, void* ws,
+                     size_t ws_bytes, const int32_t* cu_in, const int32_t* cu_out, int nseq, int H, int D, int block,
+                     int stride, int max_in, int total_out, void* stream) {
+  if (!x || !w || !dy || !cu_in || !cu_out) return fail(-1, "nsa_compress_bwd: null pointer");
+  if (stride <= 0 || block <= 0 || block % stride) return fail(-4, "nsa_compress_bwd: block must be a multiple of stride");
+  if (dw && (!ws || ws_bytes < nsa_compress_bwd_workspace_bytes(nseq, H, D, block)))
+    return fail(-6, "nsa_compress_bwd: workspace too small");
+  CompressArgs a = {};
+  a.x = (const bf16*)x; a.w = (const bf16*)w; a.dy = (const bf16*)dy; a.dx = (bf16*)dx; a.dw = dw; a.dbias = dbias;
+  a.ws = (float*)ws; a.cu_in = cu_in; a.cu_out = cu_out; a.nseq = nseq; a.H = H; a.D = D; a.l = block; a.d = stride;
+  a.max_in = max_in; a.total_out = total_out;
+  return launch_compress_bwd(a, (cudaStream_t)stream);
+}
+
+// ---- compressed attention ---------------------------------------------------------------------------
+int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
+                     float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
+                     float scale, int n_sel, int pool_k, int pool_s, int pool_p, void* stream) {
+  if (!q || !ck || !cv || !o || !lse) return fail(-1, "nsa_cmp_attn_fwd: null pointer");
+  int rc = check_attn_shape("nsa_cmp_attn_fwd", B, T, Hq, Hk, D);
+  if (rc) return rc;
+  if (Tc <= 0) return fail(-1, "nsa_cmp_attn_fwd: no compressed positions (sequence shorter than one block)");
+  DenseArgs a = {};
+  a.mode = 1; a.q = (const bf16*)q; a.k = (const bf16*)ck; a.v = (const bf16*)cv; a.o = (bf16*)o; a.lse = lse;
+  a.B = B; a.T = T; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.cblock = block; a.cstride = stride; a.causal = causal;
+  a.scale = scale; a.n_sel = n_sel;
+  if (n_sel > 0) {
+    if (!sel_idx) return fail(-1, "nsa_cmp_attn_fwd: sel_idx is null");
+    if (Hq / Hk != 16)
+      return fail(-7, "nsa_cmp_attn_fwd: block selection needs exactly 16 query heads per KV head (got %d)", Hq / Hk);
+    if (pool_k <= 0 || pool_s <= 0 || pool_p < 0) return fail(-8, "nsa_cmp_attn_fwd: bad pooling parameters");
+    a.pool_k = pool_k; a.pool_s = pool_s; a.pool_p = pool_p;
+    a.n_pool = nsa_pool_out_len(Tc, pool_k, pool_s, pool_p);
+    a.sel_idx = sel_idx; a.sel_scores = sel_scores;
+  }
+  return launch_dense_fwd(a, D, (cudaStream_t)stream);
+}
+
+size_t nsa_cmp_attn_bwd_workspace_bytes(int B, int T, int Tc, int Hk, int D) {
+  int sl;
+  const int nseg = cmp_segments(T, &sl);
+  return (size_t)2 * nseg * B * Tc * Hk * D * sizeof(float);
+}
+
+int nsa_cmp_attn_bwd(const void* q, const void* ck, const void* cv, const float* lse, const void* dout,
+                     const float* delta, const void* gate, void* dq, int accumulate_dq, void* dck, void* dcv, void* ws,
+                     size_t ws_bytes, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
+                     float scale, void* stream) {
+  if (!q || !ck || !cv || !lse || !dout || !delta) return fail(-1, "nsa_cmp_attn_bwd: null pointer");
+  int rc = check_attn_shape("nsa_cmp_attn_bwd", B, T, Hq, Hk, D);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dq) {
+    DenseArgs a = {};
+    a.mode = 1; a.q = (const bf16*)q; a.k = (const bf16*)ck; a.v = (const bf16*)cv; a.lse = const_cast<float*>(lse);
+    a.dout = (const bf16*)dout; a.delta = delta; a.gate = (const bf16*)gate; a.dq = (bf16*)dq;
+    a.accumulate = accumulate_dq; a.B = B; a.T = T; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.cblock = block;
+    a.cstride = stride; a.causal = causal; a.scale = scale;
+    rc = launch_dense_dq(a, D, s);
+    if (rc) return rc;
+  }
+  if (dck || dcv) {
+    if (!dck || !dcv) return fail(-1, "nsa_cmp_attn_bwd: dck and dcv must be given together");
+    if (!ws || ws_bytes < nsa_cmp_attn_bwd_workspace_bytes(B, T, Tc, Hk, D))
+      return fail(-6, "nsa_cmp_attn_bwd: workspace too small");
+    KvArgs a = {};
+    a.mode = 1; a.q = (const bf16*)q; a.k = (const bf16*)ck; a.v = (const bf16*)cv;
+    a.dout_a = (const bf16*)dout; a.lse_a = lse; a.delta_a = delta; a.gate_a = (const bf16*)gate;
+    a.part = (float*)ws; a.nseg = cmp_segments(T, &a.seg_len);
+    a.B = B; a.T = T; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.BS = 64; a.cblock = block; a.cstride = stride;
+    a.causal = causal; a.scale = scale;
+    rc = launch_kv_bwd(a, D, s);
+    if (rc) return rc;
+    const long long N = (long long)B * Tc * Hk * D;
+    rc = launch_reduce_segments(a.part, (bf16*)dck, a.nseg, N, T, Tc, Hk, D, a.seg_len, block, stride, causal, s);
+    if (rc) return rc;
+    rc = launch_reduce_segments(a.part + (long long)a.nseg * N, (bf16*)dcv, a.nseg, N, T, Tc, Hk, D, a.seg_len, block,
+                                stride, causal, s);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// ---- selected + sliding window ----------------------------------------------------------------------
+static int check_bs(const char* who, int BS) {
+  if (BS != 16 && BS != 32 && BS != 64) return fail(-9, "%s: selection block size %d not supported (16, 32, 64)", who, BS);
+  return 0;
+}
+
+int nsa_sel_swa_fwd(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                    void* o_slc, float* lse_slc, void* o_swa, float* lse_swa, const void* g_slc, const void* g_swa,
+                    const void* o_cmp, const void* g_cmp, void* o, int B, int T, int Hq, int Hkv, int D, int S, int BS,
+                    int window, float scale, void* stream) {
+  if (!q || !k || !v) return fail(-1, "nsa_sel_swa_fwd: null pointer");
+  int rc = check_attn_shape("nsa_sel_swa_fwd", B, T, Hq, Hkv, D);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (o_slc) {
+    if (!idx || !lse_slc) return fail(-1, "nsa_sel_swa_fwd: idx / lse_slc is null");
+    rc = check_bs("nsa_sel_swa_fwd", BS);
+    if (rc) return rc;
+    if (S <= 0) return fail(-1, "nsa_sel_swa_fwd: no selected blocks");
+    SelArgs a = {};
+    a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64; a.counts = counts;
+    a.o = (bf16*)o_slc; a.lse = lse_slc; a.B = B; a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS; a.scale = scale;
+    rc = launch_sel_fwd(a, D, s);
+    if (rc) return rc;
+  }
+  if (window > 0) {
+    if (!o_swa || !lse_swa) return fail(-1, "nsa_sel_swa_fwd: o_swa / lse_swa is null");
+    DenseArgs a = {};
+    a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.o = (bf16*)o_swa; a.lse = lse_swa;
+    a.B = B; a.T = T; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
+    rc = launch_dense_fwd(a, D, s);
+    if (rc) return rc;
+  }
+  if (o) {
+    rc = launch_combine((const bf16*)o_slc, (const bf16*)g_slc, window > 0 ? (const bf16*)o_swa : nullptr,
+                        (const bf16*)g_swa, (const bf16*)o_cmp, (const bf16*)g_cmp, (bf16*)o, (long long)B * T * Hq, D, s);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS) {
+  if (BS <= 0) return 0;
+  const size_t NB = (size_t)(T + BS - 1) / BS;
+  const size_t bh = (size_t)B * Hkv;
+  return align_up(bh * NB * NB * 4, 256) + align_up(bh * (NB + 1) * 4, 256) + align_up(bh * (size_t)T * S * 4, 256);
+}
+
+int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                    const void* dout_slc, const float* lse_slc, const float* delta_slc, const void* gate_slc,
+                    const void* dout_swa, const float* lse_swa, const float* delta_swa, const void* gate_swa, void* dq,
+                    int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
+                    int D, int S, int BS, int window, float scale, void* stream) {
+  if (!q || !k || !v) return fail(-1, "nsa_sel_swa_bwd: null pointer");
+  int rc = check_attn_shape("nsa_sel_swa_bwd", B, T, Hq, Hkv, D);
+  if (rc) return rc;
+  rc = check_bs("nsa_sel_swa_bwd", BS);
+  if (rc) return rc;
+  const bool has_slc = dout_slc != nullptr, has_swa = window > 0 && dout_swa != nullptr;
+  if (!has_slc && !has_swa) return fail(-1, "nsa_sel_swa_bwd: neither branch has an upstream gradient");
+  if (has_slc && (!idx || !lse_slc || !delta_slc)) return fail(-1, "nsa_sel_swa_bwd: selected branch inputs missing");
+  if (has_swa && (!lse_swa || !delta_swa)) return fail(-1, "nsa_sel_swa_bwd: window branch inputs missing");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dq) {
+    int acc = accumulate_dq;
+    if (has_slc) {
+      SelArgs a = {};
+      a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64; a.counts = counts;
+      a.lse = const_cast<float*>(lse_slc); a.dout = (const bf16*)dout_slc; a.delta = delta_slc;
+      a.gate = (const bf16*)gate_slc; a.dq = (bf16*)dq; a.accumulate = acc;
+      a.B = B; a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS; a.scale = scale;
+      rc = launch_sel_dq(a, D, s);
+      if (rc) return rc;
+      acc = 1;
+    }
+    if (has_swa) {
+      DenseArgs a = {};
+      a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.lse = const_cast<float*>(lse_swa);
+      a.dout = (const bf16*)dout_swa; a.delta = delta_swa; a.gate = (const bf16*)gate_swa; a.dq = (bf16*)dq;
+      a.accumulate = acc; a.B = B; a.T = T; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
+      rc = launch_dense_dq(a, D, s);
+      if (rc) return rc;
+    }
+  }
+  if (dk || dv) {
+    if (!dk || !dv) return fail(-1, "nsa_sel_swa_bwd: dk and dv must be given together");
+    KvArgs a = {};
+    a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v;
+    a.B = B; a.T = T; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.BS = BS; a.window = has_swa ? window : 0; a.scale = scale;
+    a.dk = (bf16*)dk; a.dv = (bf16*)dv;
+    if (has_slc) {
+      if (!ws || ws_bytes < nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, S, BS))
+        return fail(-6, "nsa_sel_swa_bwd: workspace too small");
+      const int NB = (T + BS - 1) / BS;
+      const size_t bh = (size_t)B * Hkv;
+      char* p = (char*)ws;
+      RevArgs r = {};
+      r.idx = idx; r.idx64 = idx64; r.counts = counts; r.B = B; r.T = T; r.H = Hkv; r.S = S; r.BS = BS; r.NB = NB;
+      r.hist = (int*)p;
+      p += align_up(bh * NB * NB * 4, 256);
+      r.rev_ptr = (int*)p;
+      p += align_up(bh * (NB + 1) * 4, 256);
+      r.rev_tok = (int*)p;
+      r.cap = (long long)T * S;
+      rc = launch_build_rev(r, s);
+      if (rc) return rc;
+      a.rev_ptr = r.rev_ptr; a.rev_tok = r.rev_tok; a.rev_cap = r.cap;
+      a.dout_a = (const bf16*)dout_slc; a.lse_a = lse_slc; a.delta_a = delta_slc; a.gate_a = (const bf16*)gate_slc;
+    }
+    if (has_swa) {
+      a.dout_b = (const bf16*)dout_swa; a.lse_b = lse_swa; a.delta_b = delta_swa; a.gate_b = (const bf16*)gate_swa;
+    }
+    rc = launch_kv_bwd(a, D, s);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// ---- helpers ------------------------------------------------------------------------------------------
+int nsa_rowdot(const void* o, const void* dout, const void* gate, float* delta, void* dgate, long long rows, int D,
+               void* stream) {
+  if (!o || !dout) return fail(-1, "nsa_rowdot: null pointer");
+  return launch_rowdot((const bf16*)o, (const bf16*)dout, (const bf16*)gate, delta, (bf16*)dgate, rows, D,
+                       (cudaStream_t)stream);
+}
+
+int nsa_combine(const void* a0, const void* g0, const void* a1, const void* g1, const void* a2, const void* g2, void* o,
+                long long rows, int D, void* stream) {
+  if (!o) return fail(-1, "nsa_combine: null output");
+  return launch_combine((const bf16*)a0, (const bf16*)g0, (const bf16*)a1, (const bf16*)g1, (const bf16*)a2,
+                        (const bf16*)g2, (bf16*)o, rows, D, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,132 @@
+// Internal launcher interface between api.cu (argument checking, C-ABI) and the kernel files.
+// All pointers are device pointers; all tensors are contiguous with the layouts given below.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace nsa {
+
+// ---- selected-block attention, query-major (forward and dQ) --------------------------------
+struct SelArgs {
+  const bf16* q;       // [B,T,Hq,D]
+  const bf16* k;       // [B,T,Hkv,D]
+  const bf16* v;       // [B,T,Hkv,D]
+  const void* idx;     // [B,T,Hkv,S] int32 or int64
+  int idx64;           // 1 if idx is int64
+  const int* counts;   // [B,T,Hkv] int32 or null
+  // forward outputs / backward inputs
+  bf16* o;             // [B,T,Hq,D]
+  float* lse;          // [B,T,Hq] natural log
+  // backward
+  const bf16* dout;    // [B,T,Hq,D]
+  const float* delta;  // [B,T,Hq]
+  const bf16* gate;    // [B,T,Hq] or null: upstream gradient is gate * dout
+  bf16* dq;            // [B,T,Hq,D]
+  int accumulate;      // dq += instead of =
+  int B, T, Hq, Hkv, S, BS;
+  float scale;
+};
+int launch_sel_fwd(const SelArgs& a, int D, cudaStream_t s);
+int launch_sel_dq(const SelArgs& a, int D, cudaStream_t s);
+int sel_status(int* out);
+
+// ---- dense query-major attention: sliding window (mode 0) and compressed (mode 1) ---------
+struct DenseArgs {
+  int mode;            // 0 sliding window over k,v [B,Lk=T,Hkv,D]; 1 compressed over ck,cv [B,Lk=Tc,Hk,D]
+  const bf16* q;       // [B,T,Hq,D]
+  const bf16* k;
+  const bf16* v;
+  bf16* o;             // [B,T,Hq,D]
+  float* lse;          // [B,T,Hq] natural log; -inf for rows without a visible key
+  const bf16* dout;
+  const float* delta;
+  const bf16* gate;
+  bf16* dq;
+  int accumulate;
+  int B, T, Lk, Hq, Hk;
+  int window;          // mode 0
+  int cblock, cstride; // mode 1: key j visible to query t iff t >= j*cstride + cblock
+  int causal;          // mode 1
+  float scale;
+  // mode 1 forward only: block selection fused behind the attention
+  int n_sel;           // 0 = no selection
+  int pool_k, pool_s, pool_p, n_pool;
+  int* sel_idx;        // [B,T,Hq/16,n_sel] int32
+  float* sel_scores;   // optional [B,Hq/16,T,n_pool] fp32 dump of the pooled scores, or null
+};
+int launch_dense_fwd(const DenseArgs& a, int D, cudaStream_t s);
+int launch_dense_dq(const DenseArgs& a, int D, cudaStream_t s);
+int dense_status(int* out);
+
+// ---- key/value-major backward (dK,dV of selected + sliding window; dCK,dCV of compressed) ---
+struct KvArgs {
+  int mode;               // 0 selected (+ window) over k,v; 1 compressed
+  const bf16* q;          // [B,T,Hq,D]
+  const bf16* k;          // [B,Lk,Hk,D]
+  const bf16* v;
+  // branch A: selected (mode 0) or compressed (mode 1); branch B: sliding window (mode 0 only)
+  const bf16* dout_a;  const float* lse_a;  const float* delta_a;  const bf16* gate_a;
+  const bf16* dout_b;  const float* lse_b;  const float* delta_b;  const bf16* gate_b;
+  const int* rev_ptr;     // [B,Hk,NB+1]   mode 0: CSR over selection blocks
+  const int* rev_tok;     // [B,Hk,cap]    tokens ascending inside each block's list
+  long long rev_cap;
+  bf16* dk;               // [B,Lk,Hk,D]
+  bf16* dv;
+  float* part;            // mode 1 workspace: [2][nseg][B,Lk,Hk,D] fp32
+  int nseg, seg_len;
+  int B, T, Lk, Hq, Hk, BS, window;
+  int cblock, cstride, causal;
+  float scale;
+};
+int launch_kv_bwd(const KvArgs& a, int D, cudaStream_t s);
+int kv_status(int* out);
+
+// ---- compression ------------------------------------------------------------------------------
+struct CompressArgs {
+  const bf16* x;        // [tok,H,D]
+  const bf16* w;        // [l*D, D]  row j*D+c, column o
+  const bf16* bias;     // [D] or null
+  bf16* y;              // [out_tok,H,D]
+  const int* cu_in;     // [nseq+1] device
+  const int* cu_out;    // [nseq+1] device
+  int nseq, H, D, l, d, max_out;   // max_out: longest compressed sequence
+  // backward
+  const bf16* dy;       // [out_tok,H,D]
+  bf16* dx;             // [tok,H,D]
+  float* dw;            // [l*D, D] fp32
+  float* dbias;         // [D] fp32 or null
+  float* ws;            // workspace for dw partials: [nseq*H][l*D*D] fp32
+  int max_in;           // longest input sequence
+  int total_out;
+};
+int launch_compress_fwd(const CompressArgs& a, cudaStream_t s);
+int launch_compress_bwd(const CompressArgs& a, cudaStream_t s);
+int compress_status(int* out);
+
+// ---- small helpers ----------------------------------------------------------------------------
+// delta[r] = (gate ? gate[r] : 1) * sum_d o[r,d]*dout[r,d];  dgate[r] = sum_d o[r,d]*dout[r,d]
+int launch_rowdot(const bf16* o, const bf16* dout, const bf16* gate, float* delta, bf16* dgate, long long rows, int D,
+                  cudaStream_t s);
+// o = g0*a0 + g1*a1 + g2*a2  (null pairs skipped); gates [rows], tensors [rows,D]
+int launch_combine(const bf16* a0, const bf16* g0, const bf16* a1, const bf16* g1, const bf16* a2, const bf16* g2,
+                   bf16* o, long long rows, int D, cudaStream_t s);
+// reverse index of the selection: for every (b,h,block) the ascending list of tokens selecting it.
+struct RevArgs {
+  const void* idx; int idx64; const int* counts;
+  int B, T, H, S, BS, NB;
+  int* hist;      // workspace [B,H,NB(chunks),NB] int32
+  int* rev_ptr;   // [B,H,NB+1]
+  int* rev_tok;   // [B,H,cap]
+  long long cap;  // T*S
+};
+int launch_build_rev(const RevArgs& a, cudaStream_t s);
+// out(bf16)[i] = sum over valid segments of part[seg][i]
+int launch_reduce_segments(const float* part, bf16* out, int nseg, long long n_per_seg, int T, int Lk, int Hk, int D,
+                           int seg_len, int cblock, int cstride, int causal, cudaStream_t s);
+int misc_status(int* out);
+
+int num_sms();
+
+}  // namespace nsa

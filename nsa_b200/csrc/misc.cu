@@ -1,0 +1,258 @@
+// Small memory-bound helpers: row dot products for the backward (delta and gate gradients), the gated
+// combine of the three branches, the reverse index of the block selection, and the fixed-order reduction
+// of the compressed branch's dCK/dCV partials.
+#include "kernels.h"
+#include "tmap.h"
+
+namespace nsa {
+
+int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+namespace {
+
+// ---- delta / gate gradient ------------------------------------------------------------------------
+// Reference: parallel_nsa_bwd_kernel_preprocess (nsa/selection_attn.py:520-530), _attn_bwd_preprocess
+// (nsa/triton_attention.py:184-199) and the autograd of the gate products (nsa/nsa.py:133,
+// nsa/selection_attn.py:808-811).  One warp per (token, head) row.
+template <int D>
+__global__ void rowdot_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dout, const bf16* __restrict__ gate,
+                              float* __restrict__ delta, bf16* __restrict__ dgate, long long rows) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  constexpr int PER = D / 32;  // 2 or 4 elements per lane
+  float acc = 0.f;
+  const bf16* po = o + row * D + lane * PER;
+  const bf16* pd = dout + row * D + lane * PER;
+#pragma unroll
+  for (int i = 0; i < PER; i += 2) {
+    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(po + i));
+    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + i));
+    acc += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    if (delta) delta[row] = gate ? acc * __bfloat162float(gate[row]) : acc;
+    if (dgate) dgate[row] = __float2bfloat16(acc);
+  }
+}
+
+// ---- gated combine ------------------------------------------------------------------------------------
+// o = g0*a0 + g1*a1 + g2*a2  (nsa/selection_attn.py:808-811 and nsa/nsa.py:133, as one pass)
+__global__ void combine_kernel(const bf16* __restrict__ a0, const bf16* __restrict__ g0, const bf16* __restrict__ a1,
+                               const bf16* __restrict__ g1, const bf16* __restrict__ a2, const bf16* __restrict__ g2,
+                               bf16* __restrict__ o, long long n8, int D8) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const long long row = i / D8;
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  auto add = [&](const bf16* a, const bf16* gp) {
+    if (!a) return;
+    const float gv = gp ? __bfloat162float(gp[row]) : 1.f;
+    const uint4 v = *reinterpret_cast<const uint4*>(a + i * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      acc[2 * k] += gv * f.x;
+      acc[2 * k + 1] += gv * f.y;
+    }
+  };
+  add(a0, g0);
+  add(a1, g1);
+  add(a2, g2);
+  uint4 out;
+  __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) ho[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+  *reinterpret_cast<uint4*>(o + i * 8) = out;
+}
+
+// ---- reverse index of the selection -----------------------------------------------------------------
+// Replaces the dense boolean block mask of parallel_nsa_kernel_mask (nsa/selection_attn.py:256-273).
+// A stable counting sort by block id in three launches; the order inside every list is ascending in t and
+// independent of scheduling, so the backward is bit-reproducible.
+__device__ __forceinline__ int rev_block(const RevArgs& a, long long row, int s, int t) {
+  int cnt = a.S;
+  if (a.counts) cnt = min(cnt, a.counts[row]);
+  if (s >= cnt) return -1;
+  long long v = a.idx64 ? reinterpret_cast<const long long*>(a.idx)[row * a.S + s]
+                        : (long long)reinterpret_cast<const int*>(a.idx)[row * a.S + s];
+  if (v < 0 || v >= a.NB || v * a.BS > t) return -1;
+  return (int)v;
+}
+
+// grid (NB chunks, B*H): histogram of the block ids selected by the BS tokens of one chunk
+__global__ void rev_hist_kernel(const RevArgs a) {
+  extern __shared__ int sh[];
+  const int chunk = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  for (int i = threadIdx.x; i < a.NB; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const int n = a.BS * a.S;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    const int t = chunk * a.BS + e / a.S, s = e % a.S;
+    if (t >= a.T) continue;
+    const int blk = rev_block(a, ((long long)b * a.T + t) * a.H + h, s, t);
+    if (blk >= 0) atomicAdd(&sh[blk], 1);
+  }
+  __syncthreads();
+  int* out = a.hist + ((long long)bh * a.NB + chunk) * a.NB;
+  for (int i = threadIdx.x; i < a.NB; i += blockDim.x) out[i] = sh[i];
+}
+
+// grid (B*H): per block id, exclusive prefix over chunks (in place) and the CSR row pointers
+__global__ void rev_scan_kernel(const RevArgs a) {
+  extern __shared__ int tot[];
+  const int bh = blockIdx.x;
+  int* hist = a.hist + (long long)bh * a.NB * a.NB;
+  for (int blk = threadIdx.x; blk < a.NB; blk += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < a.NB; ++c) {
+      const int v = hist[(long long)c * a.NB + blk];
+      hist[(long long)c * a.NB + blk] = run;
+      run += v;
+    }
+    tot[blk] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* rp = a.rev_ptr + (long long)bh * (a.NB + 1);
+    int run = 0;
+    for (int blk = 0; blk < a.NB; ++blk) {
+      rp[blk] = run;
+      run += tot[blk];
+    }
+    rp[a.NB] = run;
+  }
+}
+
+// grid (NB chunks, B*H), one warp: write the tokens of the chunk, in order, behind each block's cursor
+__global__ void rev_fill_kernel(const RevArgs a) {
+  extern __shared__ int cur[];
+  const int chunk = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int lane = threadIdx.x;
+  const int* rp = a.rev_ptr + (long long)bh * (a.NB + 1);
+  const int* pre = a.hist + ((long long)bh * a.NB + chunk) * a.NB;
+  for (int i = lane; i < a.NB; i += 32) cur[i] = rp[i] + pre[i];
+  __syncwarp();
+  int* out = a.rev_tok + (long long)bh * a.cap;
+  for (int tt = 0; tt < a.BS; ++tt) {
+    const int t = chunk * a.BS + tt;
+    if (t >= a.T) break;
+    const long long row = ((long long)b * a.T + t) * a.H + h;
+    for (int s0 = 0; s0 < a.S; s0 += 32) {
+      const int s = s0 + lane;
+      const int blk = (s < a.S) ? rev_block(a, row, s, t) : -1;
+      const int key = blk >= 0 ? blk : -1 - lane;  // invalid lanes never match each other
+      const unsigned same = __match_any_sync(0xffffffffu, key);
+      if (blk >= 0) {
+        const int rank = __popc(same & ((1u << lane) - 1));
+        const int pos = cur[blk] + rank;
+        if (pos < a.cap) out[pos] = t;
+      }
+      __syncwarp();
+      if (blk >= 0 && (lane == 31 || (same >> (lane + 1)) == 0)) cur[blk] += __popc(same);  // highest lane of the group
+      __syncwarp();
+    }
+  }
+}
+
+// ---- fixed-order reduction of segment partials ----------------------------------------------------------
+__global__ void reduce_segments_kernel(const float* __restrict__ part, bf16* __restrict__ out, int nseg,
+                                       long long n_per_seg, int T, int Lk, int HkD, int seg_len, int cblock,
+                                       int cstride, int causal) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (i >= n_per_seg) return;
+  const int j = (int)((i / HkD) % Lk);
+  const int first = causal ? (j / 64) * 64 * cstride + cblock : 0;
+  float x = 0.f, y = 0.f;
+  for (int seg = 0; seg < nseg; ++seg) {
+    const int lo = max(first, seg * seg_len), hi = min(T, (seg + 1) * seg_len);
+    if (hi <= lo) continue;
+    const float2 v = *reinterpret_cast<const float2*>(part + (long long)seg * n_per_seg + i);
+    x += v.x;
+    y += v.y;
+  }
+  *reinterpret_cast<__nv_bfloat162*>(out + i) = __floats2bfloat162_rn(x, y);
+}
+
+}  // namespace
+
+int launch_rowdot(const bf16* o, const bf16* dout, const bf16* gate, float* delta, bf16* dgate, long long rows, int D,
+                  cudaStream_t s) {
+  if (rows <= 0) return 0;
+  const int wpb = 8;
+  const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
+  if (D == 128)
+    rowdot_kernel<128><<<grid, wpb * 32, 0, s>>>(o, dout, gate, delta, dgate, rows);
+  else if (D == 64)
+    rowdot_kernel<64><<<grid, wpb * 32, 0, s>>>(o, dout, gate, delta, dgate, rows);
+  else {
+    set_error("head_dim %d not supported (64 or 128)", D);
+    return -2;
+  }
+  return (int)cudaGetLastError();
+}
+
+int launch_combine(const bf16* a0, const bf16* g0, const bf16* a1, const bf16* g1, const bf16* a2, const bf16* g2,
+                   bf16* o, long long rows, int D, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (D % 8) {
+    set_error("head_dim must be a multiple of 8");
+    return -2;
+  }
+  const long long n8 = rows * (D / 8);
+  combine_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, s>>>(a0, g0, a1, g1, a2, g2, o, n8, D / 8);
+  return (int)cudaGetLastError();
+}
+
+int launch_build_rev(const RevArgs& a, cudaStream_t s) {
+  if (a.B <= 0 || a.T <= 0) return 0;
+  if ((size_t)a.NB * 4 > 200 * 1024) {
+    set_error("reverse index: too many selection blocks (%d)", a.NB);
+    return -34;
+  }
+  const dim3 grid(a.NB, a.B * a.H);
+  const size_t sm = (size_t)a.NB * 4;
+  if (sm > 48 * 1024) {
+    cudaFuncSetAttribute(rev_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    cudaFuncSetAttribute(rev_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    cudaFuncSetAttribute(rev_fill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  }
+  rev_hist_kernel<<<grid, 128, sm, s>>>(a);
+  rev_scan_kernel<<<a.B * a.H, 256, sm, s>>>(a);
+  rev_fill_kernel<<<grid, 32, sm, s>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int launch_reduce_segments(const float* part, bf16* out, int nseg, long long n_per_seg, int T, int Lk, int Hk, int D,
+                           int seg_len, int cblock, int cstride, int causal, cudaStream_t s) {
+  if (n_per_seg <= 0) return 0;
+  const long long pairs = n_per_seg / 2;
+  reduce_segments_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(part, out, nseg, n_per_seg, T, Lk, Hk * D,
+                                                                          seg_len, cblock, cstride, causal);
+  return (int)cudaGetLastError();
+}
+
+int misc_status(int* out) {
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_dev_error, sizeof(int));
+  if (e == cudaSuccess && *out) e = cudaMemcpyToSymbol(g_dev_error, &zero, sizeof(int));
+  return (int)e;
+}
+
+}  // namespace nsa

@@ -164,29 +164,34 @@ def cmp_attention(q: torch.Tensor, ck: torch.Tensor, cv: torch.Tensor, stride: i
 
 
 def selected_attention(q, k, v, block_indices, block_counts=None, block_size: int = 64,
-                       scale: Optional[float] = None, chunk: int = 128):
+                       scale: Optional[float] = None, chunk: int = 128, q_pos=None):
     """Attention of every query over the keys of its selected blocks.
     A key at position p of block b (p = b*block_size + r) takes part iff b >= 0, p <= t and the
     slot is below ``block_counts``; a query with no valid key gives 0 (the reference's NaN -> 0
     convention).  Follows naive_nsa, tests/test_parallel_nsa.py:81-144 and :207-212, and the
     skip rule of nsa/selection_attn.py:454,464.
-    q [B,T,Hq,D]; k,v [B,T,Hkv,D]; block_indices [B,T,Hkv,S].  Returns (o fp32, lse fp32)."""
-    B, T, Hq, D = q.shape
+    q [B,T,Hq,D]; k,v [B,T,Hkv,D]; block_indices [B,T,Hkv,S].  Returns (o fp32, lse fp32).
+    ``q_pos`` (optional, [Tq]) gives the sequence positions of the query rows when q holds only a
+    subset of the rows (row-sampled checks at full size); k,v always hold the whole sequence."""
+    B, Tq, Hq, D = q.shape
+    T = k.shape[1]
+    if q_pos is None:
+        q_pos = torch.arange(Tq)
     Hkv = k.shape[2]
     G = Hq // Hkv
     S = block_indices.shape[-1]
     if scale is None:
         scale = D ** -0.5
     qf, kf, vf = q.float(), k.float(), v.float()
-    o = qf.new_zeros(B, T, Hq, v.shape[-1])
-    lse = qf.new_full((B, T, Hq), float("-inf"))
+    o = qf.new_zeros(B, Tq, Hq, v.shape[-1])
+    lse = qf.new_full((B, Tq, Hq), float("-inf"))
     r = torch.arange(block_size)
     for b in range(B):
-        for t0 in range(0, T, chunk):
-            t1 = min(T, t0 + chunk)
+        for t0 in range(0, Tq, chunk):
+            t1 = min(Tq, t0 + chunk)
             idx = block_indices[b, t0:t1].long()                                # [c,Hkv,S]
             pos = idx.unsqueeze(-1) * block_size + r                           # [c,Hkv,S,bs]
-            tt = torch.arange(t0, t1).view(-1, 1, 1, 1)
+            tt = q_pos[t0:t1].view(-1, 1, 1, 1)
             bad = (idx.unsqueeze(-1) < 0) | (pos > tt)
             if block_counts is not None:
                 if torch.is_tensor(block_counts):

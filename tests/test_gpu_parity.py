@@ -1,0 +1,361 @@
+"""GPU parity tests: the CUDA kernels (reached through the C ABI via the nsa_b200 package) against the CPU
+oracle and against the golden fixtures made from the reference's own functions.
+
+Tolerance (outputs and gradients, bf16 kernels vs fp32 oracle on identical bf16-representable inputs):
+2e-2 absolute / 1e-2 relative.  Selected block index sets must equal the oracle's except where the oracle
+score is within 1e-3 of its n-th largest score.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import nsa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 2e-2, 1e-2
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda"
+
+
+def _gold(name):
+    d = np.load(os.path.join(GOLD, name + ".npz"))
+    return {k: torch.from_numpy(np.asarray(d[k])) for k in d.files}
+
+
+def _dev(x):
+    return x.to(DEV, torch.bfloat16)
+
+
+def _close(name, got, ref, atol=ATOL, rtol=RTOL):
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    assert got.shape == ref.shape, "%s: shape %s vs %s" % (name, tuple(got.shape), tuple(ref.shape))
+    assert not torch.isnan(got).any(), "%s: NaN in kernel output" % name
+    err = (got - ref).abs()
+    bad = err > atol + rtol * ref.abs()
+    assert not bad.any(), "%s: %d/%d outside tolerance, max abs err %.4g (ref max %.4g)" % (
+        name, int(bad.sum()), bad.numel(), float(err.max()), float(ref.abs().max()))
+
+
+@pytest.fixture(scope="module")
+def nsa():
+    import nsa_b200
+    yield nsa_b200
+    nsa_b200._lib.device_status()
+
+
+def _r(x):
+    return x.bfloat16().float()
+
+
+# ------------------------------------------------------------------------------------------------------
+# golden fixtures (outputs of the reference's own functions)
+# ------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", cases.CMP_CASES)
+def test_cmp_attention_golden(nsa, name):
+    c, g = cases.cmp_case(name), _gold(name)
+    q, ck, cv = (_dev(c[k]).requires_grad_(True) for k in ("q", "ck", "cv"))
+    o, idx = nsa.triton_attention.flash_attn_func(q, ck, cv, c["stride"], c["block"], True, None, c["Hkv"],
+                                                  c["pool_kernel"], c["pool_stride"], c["pool_pad"], c["n"])
+    _close("o", o, g["o"])
+    sc = O.pooled_scores(c["q"], c["ck"], c["Hkv"], c["pool_kernel"], c["pool_stride"], c["pool_pad"])
+    hard, soft = O.index_sets_match(idx.cpu(), sc, c["n"], gap=1e-3)
+    assert hard == 0, "%d rows select a block outside the 1e-3 waiver (%d rows differ at all)" % (hard, soft)
+    o.backward(_dev(c["do"]))
+    _close("dq", q.grad, g["dq"])
+    _close("dck", ck.grad, g["dck"])
+    _close("dcv", cv.grad, g["dcv"])
+    nsa._lib.device_status()
+
+
+@pytest.mark.parametrize("name", cases.SEL_CASES)
+def test_selection_golden(nsa, name):
+    c, g = cases.sel_case(name), _gold(name)
+    q, k, v = (_dev(c[x]).requires_grad_(True) for x in ("q", "k", "v"))
+    o = nsa.selection_attention(q, k, v, _dev(c["g_slc"]), _dev(c["g_swa"]), c["idx"].to(DEV), c["counts"].to(DEV),
+                                c["block_size"], c["window"])
+    _close("o", o, g["o"])
+    if c["window"] > 0:
+        o.backward(_dev(c["do"]))
+        _close("dq", q.grad, g["dq"])
+        _close("dk", k.grad, g["dk"])
+        ok = ~torch.isnan(g["dv"])          # the reference's dv holds NaN at keys of its empty-selection rows
+        _close("dv", torch.where(ok, v.grad.float().cpu(), torch.zeros(())), torch.nan_to_num(g["dv"], nan=0.0))
+    nsa._lib.device_status()
+
+
+@pytest.mark.parametrize("name", cases.COMPRESS_CASES)
+def test_compression_golden(nsa, name):
+    c, g = cases.compress_case(name), _gold(name)
+    x = _dev(c["x"]).requires_grad_(True)
+    w = _dev(c["w"]).requires_grad_(True)
+    cu = torch.tensor(c["cu"], dtype=torch.int32, device=DEV)
+    ck, cv, cu_out = nsa.compression_kv.compress_kv(x, x, w, w, cu, c["stride"], c["block"])
+    _close("y", ck, g["y"])
+    _close("y(v)", cv, g["y"])
+    n = nsa.compression_kv.calc_compressed_len(c["T"], c["stride"], c["block"])
+    assert cu_out.tolist() == [n * i for i in range(c["B"] + 1)]
+    tgt = torch.sin(torch.arange(ck.numel(), dtype=torch.float32)).reshape(ck.shape)
+    ck.backward(_dev(tgt))
+    # the kernel sees the bf16-rounded upstream gradient; the golden used the fp32 one
+    _close("dx", x.grad, g["dx"], atol=3e-2)
+    _close("dw", w.grad, g["dw"], atol=6e-2, rtol=2e-2)
+    comp = nsa.compression_kv.KVCompressor(c["stride"], c["block"], x.shape[-1], DEV, torch.bfloat16)
+    with torch.no_grad():
+        comp.compressor_k.weight.copy_(c["conv_w"])
+        comp.compressor_k.bias.copy_(c["conv_b"])
+        comp.compressor_v.weight.copy_(c["conv_w"].flip(0))
+        comp.compressor_v.bias.copy_(c["conv_b"].flip(0))
+    yk, yv, _ = comp(_dev(c["x"]), _dev(c["x"] * 0.5), cu, None)
+    _close("conv_k", yk, g["conv_k"])
+    _close("conv_v", yv, g["conv_v"])
+    nsa._lib.device_status()
+
+
+# ------------------------------------------------------------------------------------------------------
+# oracle comparisons at D = 128 / larger shapes, forward and backward
+# ------------------------------------------------------------------------------------------------------
+def _rand_indices(B, T, H, S, BS, gen, poison=True):
+    idx = torch.full((B, T, H, S), -1, dtype=torch.long)
+    for b in range(B):
+        for t in range(T):
+            for h in range(H):
+                nblk = t // BS + 1
+                perm = torch.randperm(nblk, generator=gen)[:S]
+                idx[b, t, h, :len(perm)] = perm
+    if poison:
+        idx[0, 5, 0, :] = T // BS            # only future blocks: empty selection
+        idx[-1, T - 1, -1, 0] = (T - 1) // BS  # make sure the local block is present somewhere
+    return idx
+
+
+@pytest.mark.parametrize("D,BS,S,Hq,Hkv,T,window", [(128, 64, 4, 32, 2, 384, 100), (64, 32, 5, 16, 1, 200, 0),
+                                                    (128, 16, 3, 16, 1, 130, 33)])
+def test_selection_and_window_fwd_bwd(nsa, D, BS, S, Hq, Hkv, T, window):
+    gen = torch.Generator().manual_seed(1234 + D + BS)
+    B = 2
+    q = _r(torch.randn(B, T, Hq, D, generator=gen))
+    k = _r(torch.randn(B, T, Hkv, D, generator=gen))
+    v = _r(torch.randn(B, T, Hkv, D, generator=gen))
+    do_slc = _r(torch.randn(B, T, Hq, D, generator=gen))
+    do_swa = _r(torch.randn(B, T, Hq, D, generator=gen))
+    idx = _rand_indices(B, T, Hkv, S, BS, gen)
+    counts = torch.randint(1, S + 1, (B, T, Hkv), generator=gen)
+    qd, kd, vd = (_dev(x).requires_grad_(True) for x in (q, k, v))
+    o_slc, o_swa = nsa.selection_attn.ParallelNSAFunction.apply(qd, kd, vd, idx.to(DEV), counts.to(DEV), BS, window,
+                                                                D ** -0.5, None)
+    qo, ko, vo = (x.clone().requires_grad_(True) for x in (q, k, v))
+    r_slc, r_lse = O.selected_attention(qo, ko, vo, idx, counts, BS)
+    _close("o_slc", o_slc, r_slc)
+    loss_k = (o_slc.float() * _dev(do_slc).float()).sum()
+    loss_o = (r_slc * do_slc).sum()
+    if window > 0:
+        r_swa, _ = O.sliding_window_attention(qo, ko, vo, window)
+        _close("o_swa", o_swa, r_swa)
+        loss_k = loss_k + (o_swa.float() * _dev(do_swa).float()).sum()
+        loss_o = loss_o + (r_swa * do_swa).sum()
+    loss_k.backward()
+    loss_o.backward()
+    _close("dq", qd.grad, qo.grad)
+    _close("dk", kd.grad, ko.grad)
+    _close("dv", vd.grad, vo.grad)
+    nsa._lib.device_status()
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,T,block,stride", [(128, 32, 2, 520, 32, 16), (64, 16, 1, 333, 64, 16)])
+def test_cmp_attention_fwd_bwd(nsa, D, Hq, Hkv, T, block, stride):
+    gen = torch.Generator().manual_seed(77 + D)
+    B, sel_block, n = 2, 64, 3
+    Tc = (T - block) // stride + 1
+    q = _r(torch.randn(B, T, Hq, D, generator=gen))
+    ck = _r(torch.randn(B, Tc, Hkv, D, generator=gen) * 0.5)
+    cv = _r(torch.randn(B, Tc, Hkv, D, generator=gen))
+    do = _r(torch.randn(B, T, Hq, D, generator=gen))
+    pk, ps, pp = sel_block // stride + 1, sel_block // stride, block // stride - 2
+    qd, kd, vd = (_dev(x).requires_grad_(True) for x in (q, ck, cv))
+    o, idx = nsa.triton_attention.flash_attn_func(qd, kd, vd, stride, block, True, None, Hkv, pk, ps, pp, n)
+    qo, ko, vo = (x.clone().requires_grad_(True) for x in (q, ck, cv))
+    ro, _ = O.cmp_attention(qo, ko, vo, stride, block, True)
+    _close("o_cmp", o, ro)
+    sc = O.pooled_scores(q, ck, Hkv, pk, ps, pp)
+    hard, soft = O.index_sets_match(idx.cpu(), sc, n, gap=1e-3)
+    assert hard == 0, "%d rows select a block outside the 1e-3 waiver (%d differ)" % (hard, soft)
+    o.backward(_dev(do))
+    (ro * do).sum().backward()
+    _close("dq", qd.grad, qo.grad)
+    _close("dck", kd.grad, ko.grad)
+    _close("dcv", vd.grad, vo.grad)
+    # the reference's repeated-head calling convention gives the same result
+    o2, idx2 = nsa.triton_attention.flash_attn_func(_dev(q), _dev(ck).repeat_interleave(Hq // Hkv, 2),
+                                                    _dev(cv).repeat_interleave(Hq // Hkv, 2), stride, block, True, None,
+                                                    Hkv, pk, ps, pp, n)
+    assert torch.equal(o2, o) and torch.equal(idx2, idx)
+    nsa._lib.device_status()
+
+
+def test_pooled_scores_dump_matches_oracle(nsa):
+    """The fused score path (never written to HBM in production) can be dumped for inspection."""
+    from nsa_b200 import _lib
+    gen = torch.Generator().manual_seed(5)
+    B, T, Hq, Hkv, D, block, stride = 1, 1024, 16, 1, 128, 32, 16
+    Tc = (T - block) // stride + 1
+    q = _r(torch.randn(B, T, Hq, D, generator=gen) * 0.3)
+    ck = _r(torch.randn(B, Tc, Hkv, D, generator=gen) * 0.3)
+    L = _lib.lib()
+    n_pool = L.nsa_pool_out_len(Tc, 5, 4, 0)
+    assert n_pool == T // 64
+    qd, kd = _dev(q), _dev(ck)
+    o = torch.empty_like(qd)
+    lse = torch.empty(B, T, Hq, dtype=torch.float32, device=DEV)
+    idx = torch.empty(B, T, Hkv, 16, dtype=torch.int32, device=DEV)
+    scores = torch.empty(B, Hkv, T, n_pool, dtype=torch.float32, device=DEV)
+    _lib.check(L.nsa_cmp_attn_fwd(_lib.ptr(qd), _lib.ptr(kd), _lib.ptr(kd), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(idx),
+                                  _lib.ptr(scores), B, T, Tc, Hq, Hkv, D, block, stride, 1, D ** -0.5, 16, 5, 4, 0,
+                                  _lib.stream()), "nsa_cmp_attn_fwd")
+    ref = O.pooled_scores(q, ck, Hkv, 5, 4, 0)
+    _close("pooled scores", scores, ref, atol=2e-3, rtol=1e-2)
+    # T = 1024 has exactly 16 pooled blocks, so top-16 selects every block (BASELINE config 1's shape)
+    assert (idx.sort(-1)[0].cpu() == torch.arange(16).view(1, 1, 1, 16)).all()
+    _lib.device_status()
+
+
+@pytest.mark.parametrize("D,H,block,stride,lens", [(128, 2, 32, 16, [256, 100, 48, 31]), (64, 3, 64, 16, [200, 64])])
+def test_compression_varlen_fwd_bwd(nsa, D, H, block, stride, lens):
+    gen = torch.Generator().manual_seed(9 + D)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    x = _r(torch.randn(cu[-1], H, D, generator=gen))
+    w = _r(torch.randn(block * D, D, generator=gen) * 0.03)
+    xd, wd = _dev(x).requires_grad_(True), _dev(w).requires_grad_(True)
+    ck, cv, cu_out = nsa.compression_kv.compress_kv(xd, xd, wd, wd, torch.tensor(cu, dtype=torch.int32, device=DEV),
+                                                    stride, block)
+    xo, wo = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    ry, rcu = O.compress_varlen(xo, wo, cu, block, stride)
+    assert cu_out.tolist() == rcu
+    _close("y", ck, ry)
+    dy = _r(torch.randn(ry.shape, generator=gen))
+    ck.backward(_dev(dy))
+    (ry * dy).sum().backward()
+    _close("dx", xd.grad, xo.grad)
+    _close("dw", wd.grad, wo.grad, atol=5e-2, rtol=2e-2)
+    nsa._lib.device_status()
+
+
+def _module_and_oracle(nsa, B, T, Hq, Hkv, D, n_sel, window, seed):
+    gen = torch.Generator().manual_seed(seed)
+    q = _r(torch.randn(B, T, Hq, D, generator=gen))
+    k = _r(torch.randn(B, T, Hkv, D, generator=gen))
+    v = _r(torch.randn(B, T, Hkv, D, generator=gen))
+    mod = nsa.NSAAttention(D, True, None, 0.0, selected_block_count=n_sel, sliding_window=window, device=DEV,
+                           dtype=torch.bfloat16)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.copy_(_r(torch.randn(p.shape, generator=gen) * 0.02))
+        mod.gating.bias.copy_(_r(torch.tensor([0.5, 0.4, 0.6])))
+    return mod, q, k, v, gen
+
+
+def _oracle_module_forward(mod, q, k, v, indices, ck, cv, window):
+    """The oracle composition evaluated with the kernel's own compressed K/V (bf16) and selected indices, so the
+    comparison is not confounded by near-tie selections; both are checked separately against the oracle."""
+    wg, bg = mod.gating.weight.detach().float().cpu(), mod.gating.bias.detach().float().cpu()
+    o_cmp, _ = O.cmp_attention(q, ck, cv, mod.compression_stride, mod.compression_block, True)
+    o_slc, _ = O.selected_attention(q, k, v, indices, None, mod.selection_block_size)
+    o_swa, _ = O.sliding_window_attention(q, k, v, window)
+    gate = _r(q.float() @ wg.t() + bg)          # the module's gates are bf16 tensors
+    return o_slc * gate[..., 0:1] + o_swa * gate[..., 1:2] + o_cmp * gate[..., 2:3]
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,T,n_sel,window", [(128, 32, 2, 1024, 4, 128), (64, 16, 1, 640, 3, 64)])
+def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window):
+    B = 2
+    mod, q, k, v, gen = _module_and_oracle(nsa, B, T, Hq, Hkv, D, n_sel, window, seed=31 + D)
+    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
+    qd, kd, vd = (_dev(x.reshape(B * T, *x.shape[2:])).requires_grad_(True) for x in (q, k, v))
+    out = mod(qd, kd, vd, cu, T)
+    assert out.shape == (B * T, Hq, D)
+    # stage 1: compression against the oracle
+    ckd, cvd, _ = mod.compressor(kd.detach(), vd.detach(), cu, None)
+    wk, bk = mod.compressor.compressor_k.weight.detach().float().cpu(), mod.compressor.compressor_k.bias.detach().float().cpu()
+    wv, bv = mod.compressor.compressor_v.weight.detach().float().cpu(), mod.compressor.compressor_v.bias.detach().float().cpu()
+    _close("ck", ckd, O.compress_conv(k, wk, bk, 32, 16))
+    _close("cv", cvd, O.compress_conv(v, wv, bv, 32, 16))
+    # stage 2: indices against the oracle scores on the kernel's compressed keys
+    ck_b, cv_b = ckd.float().cpu(), cvd.float().cpu()
+    _, idx = nsa.triton_attention.flash_attn_func(qd.detach().view(B, T, Hq, D), ckd, cvd, 16, 32, True, None, Hkv, 5, 4,
+                                                  0, n_sel)
+    sc = O.pooled_scores(q, ck_b, Hkv, 5, 4, 0)
+    hard, soft = O.index_sets_match(idx.cpu(), sc, n_sel, gap=1e-3)
+    assert hard == 0, "%d rows outside the waiver (%d differ)" % (hard, soft)
+    # stage 3: the whole forward and backward with indices fixed to the kernel's
+    qo, ko, vo = (x.clone().requires_grad_(True) for x in (q, k, v))
+    wk_o, bk_o, wv_o, bv_o = (t.clone().requires_grad_(True) for t in (wk, bk, wv, bv))
+    ck_o = O.compress_conv(ko, wk_o, bk_o, 32, 16)
+    cv_o = O.compress_conv(vo, wv_o, bv_o, 32, 16)
+    wg_o = mod.gating.weight.detach().float().cpu().requires_grad_(True)
+    bg_o = mod.gating.bias.detach().float().cpu().requires_grad_(True)
+    o_cmp, _ = O.cmp_attention(qo, ck_o, cv_o, 16, 32, True)
+    o_slc, _ = O.selected_attention(qo, ko, vo, idx.cpu(), None, 64)
+    o_swa, _ = O.sliding_window_attention(qo, ko, vo, window)
+    gate = qo @ wg_o.t() + bg_o
+    ref = o_slc * gate[..., 0:1] + o_swa * gate[..., 1:2] + o_cmp * gate[..., 2:3]
+    _close("module output", out.view(B, T, Hq, D), ref, atol=3e-2)
+    do = _r(torch.randn(B, T, Hq, D, generator=gen))
+    out.backward(_dev(do.reshape(B * T, Hq, D)))
+    (ref * do).sum().backward()
+    _close("dq", qd.grad.view(B, T, Hq, D), qo.grad, atol=4e-2, rtol=2e-2)
+    _close("dk", kd.grad.view(B, T, Hkv, D), ko.grad, atol=4e-2, rtol=2e-2)
+    _close("dv", vd.grad.view(B, T, Hkv, D), vo.grad, atol=4e-2, rtol=2e-2)
+    _close("d gating.weight", mod.gating.weight.grad, wg_o.grad, atol=0.5, rtol=3e-2)
+    _close("d conv_k.weight", mod.compressor.compressor_k.weight.grad, wk_o.grad, atol=0.5, rtol=5e-2)
+    _close("d conv_v.bias", mod.compressor.compressor_v.bias.grad, bv_o.grad, atol=0.5, rtol=5e-2)
+    nsa._lib.device_status()
+
+
+# ------------------------------------------------------------------------------------------------------
+# full-size properties (BASELINE.json config 2: B=4, T=8192, Hq=64, Hkv=4, D=128, top-16 of 64-key blocks)
+# ------------------------------------------------------------------------------------------------------
+def _config2_indices(B, T, H, S, BS, gen, device):
+    """min(S, t//BS+1) distinct causally valid blocks, always with block 0 and the local block; rest = -1."""
+    t = torch.arange(T, device=device)
+    nblk = (t // BS + 1).view(1, T, 1, 1)
+    NB = T // BS
+    r = torch.rand(B, T, H, NB, generator=gen, device=device)
+    blk = torch.arange(NB, device=device).view(1, 1, 1, NB)
+    r = torch.where(blk < nblk, r, torch.full_like(r, -1.0))
+    r = torch.where((blk == 0) | (blk == nblk - 1), torch.full_like(r, 2.0), r)
+    top = torch.topk(r, S, dim=-1)
+    return torch.where(top.values >= 0, top.indices, torch.full_like(top.indices, -1)).to(torch.int32)
+
+
+def test_selection_full_size_properties(nsa):
+    B, T, Hq, Hkv, D, S, BS = 4, 8192, 64, 4, 128, 16, 64
+    gen = torch.Generator(device=DEV).manual_seed(1)
+    q = torch.randn(B, T, Hq, D, generator=gen, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B, T, Hkv, D, generator=gen, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B, T, Hkv, D, generator=gen, device=DEV, dtype=torch.bfloat16)
+    idx = _config2_indices(B, T, Hkv, S, BS, gen, DEV)
+    ones = torch.ones(B, T, Hq, device=DEV, dtype=torch.bfloat16)
+    o = nsa.selection_attention(q, k, v, ones, ones, idx, None, BS, 0)
+    o2 = nsa.selection_attention(q, k, v, ones, ones, idx, None, BS, 0)
+    assert torch.equal(o, o2), "two runs differ: the kernel is not deterministic"
+    # soft-max weights sum to one: with V = 1 every row (all have a valid key here) is exactly 1
+    o1 = nsa.selection_attention(q, k, torch.ones_like(v), ones, ones, idx, None, BS, 0)
+    assert (o1.float() - 1).abs().max() < 1e-2
+    # linearity in V
+    v2 = torch.randn_like(v)
+    oa = nsa.selection_attention(q, k, (v + v2), ones, ones, idx, None, BS, 0).float()
+    ob = nsa.selection_attention(q, k, v2, ones, ones, idx, None, BS, 0).float()
+    assert (oa - (o.float() + ob)).abs().max() < 6e-2
+    # sampled rows against the oracle
+    rows = [(0, 0), (0, 63), (1, 64), (2, 4097), (3, 8191), (1, 1000)]
+    kc, vc = k.cpu().float(), v.cpu().float()
+    for b, t in rows:
+        ref, _ = O.selected_attention(q[b:b + 1, t:t + 1].cpu().float(), kc[b:b + 1], vc[b:b + 1],
+                                      idx[b:b + 1, t:t + 1].cpu().long(), None, BS, q_pos=torch.tensor([t]))
+        _close("row (%d,%d)" % (b, t), o[b, t], ref[0, 0])
+    nsa._lib.device_status()
