@@ -1,0 +1,430 @@
+#!/usr/bin/env python
+"""Benchmark of the NSA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): BASELINE.json configs[2], the configuration its metric is quoted on -- the full NSAAttention
+module forward + backward in bf16, B=8, T=8192, Hq=64, Hkv=4, D=128, compression block 32 / stride 16,
+selection block 64, top-16, window 512, q/k/v/dO ~ N(0,1), weights ~ N(0,0.02), seed 2.  With N > 1 the batch
+is sharded over the ranks (one process per GPU, total work fixed: strong scaling) and the 1.05 M weight
+gradients are all-reduced over NCCL inside the timed region.
+
+One JSON line is printed by rank 0: whole-job tokens/s with inputs resident in HBM (`value`), the same through
+the public API from pinned host buffers with the copies timed (`e2e`), the dominant kernel's roofline
+(`roofline`, timed with CUDA events inside this run), a per-kernel breakdown, the clocks sampled under load
+and the CPU baseline (the oracle restatement of the reference's naive torch path on the host cores).
+
+`--impl reference` times that CPU restatement alone (the reference itself is Python under /root/reference,
+which does not exist on the GPU box; it has no compiled artefact that could travel).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(B=8, T=8192, Hq=64, Hkv=4, D=128, block=32, stride=16, sel_block=64, n_sel=16, window=512, seed=2)
+WORKLOAD = "configs[2]: NSAAttention module fwd+bwd bf16, B=8 T=8192 Hq=64 Hkv=4 D=128, cmp 32/16, sel 64 top-16, window 512"
+METRIC = "NSA fwd+bwd tokens/s"
+
+
+# ---------------------------------------------------------------------------------------------------------
+# algorithmic FLOPs (2 flops per MAC, causally useful work only)
+# ---------------------------------------------------------------------------------------------------------
+def flop_model(B, T, Hq, Hkv, D, block, stride, sel_block, n_sel, window, nsel_pairs=None):
+    Tc = (T - block) // stride + 1
+    nvis = sum(min(max((t - block) // stride + 1, 0), Tc) for t in range(T))
+    nsel = sum(sel_block * min(n_sel, t // sel_block + 1) for t in range(T)) if nsel_pairs is None else nsel_pairs
+    nswa = sum(min(t + 1, window) for t in range(T))
+    f = {}
+    f["cmp"] = 4.0 * D * B * Hq * nvis
+    f["slc"] = 4.0 * D * B * Hq * nsel
+    f["swa"] = 4.0 * D * B * Hq * nswa
+    f["comp"] = 2.0 * (2 * block * D * D) * B * Hkv * Tc
+    f["gate"] = 2.0 * D * 3 * B * T * Hq
+    f["fwd"] = f["cmp"] + f["slc"] + f["swa"] + f["comp"] + f["gate"]
+    f["bwd"] = 2.5 * (f["cmp"] + f["slc"] + f["swa"]) + 2 * (f["comp"] + f["gate"])
+    f["total"] = f["fwd"] + f["bwd"]
+    return f
+
+
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], tf_burst=d["bf16_tflops"], tf_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+# ---------------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for ts, line in self.rows:
+            if ts < t0 or ts > t1 + 0.3:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except Exception:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CPU arm: the oracle restatement of the reference's naive torch path
+# ---------------------------------------------------------------------------------------------------------
+def cpu_step(sample_T, steps, warmup):
+    import torch
+    from oracle import nsa_oracle as O
+    c = CFG
+    torch.set_num_threads(os.cpu_count() or 1)
+    gen = torch.Generator().manual_seed(c["seed"])
+    q = torch.randn(1, sample_T, c["Hq"], c["D"], generator=gen).bfloat16().float().requires_grad_(True)
+    k = torch.randn(1, sample_T, c["Hkv"], c["D"], generator=gen).bfloat16().float().requires_grad_(True)
+    v = torch.randn(1, sample_T, c["Hkv"], c["D"], generator=gen).bfloat16().float().requires_grad_(True)
+    do = torch.randn(1, sample_T, c["Hq"], c["D"], generator=gen)
+    wk, wv = ((torch.randn(c["D"], c["D"], c["block"], generator=gen) * 0.02).requires_grad_(True) for _ in range(2))
+    bk, bv = (torch.zeros(c["D"], requires_grad=True) for _ in range(2))
+    wg, bg = (torch.randn(3, c["D"], generator=gen) * 0.02).requires_grad_(True), torch.zeros(3, requires_grad=True)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.time()
+        o = O.nsa_forward(q, k, v, wk, bk, wv, bv, wg, bg, stride=c["stride"], block=c["block"],
+                          sel_block=c["sel_block"], n_sel=c["n_sel"], window=c["window"])
+        o.backward(do)
+        for t in (q, k, v, wk, wv, bk, bv, wg, bg):
+            t.grad = None
+        if i >= warmup:
+            times.append(time.time() - t0)
+    sec = sum(times) / len(times)
+    return dict(value=sample_T / sec, unit="tokens/s", cores=torch.get_num_threads(), kind="port",
+                sample="fwd+bwd of the fp32 oracle on 1 sequence x %d tokens of the workload (Hq=64, Hkv=4, D=128), "
+                       "%d timed step(s), %.1f s each" % (sample_T, len(times), sec)), sec
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb, sec = cpu_step(1024, max(1, min(args.steps, 3)), 1 if args.warmup > 0 else 0)
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "reference_arm": "CPU restatement (oracle) of the reference's naive "
+                       "torch path; each step is a bounded 1024-token sample of the workload"},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------
+def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
+    """Times every kernel family of the step separately with CUDA events on the current stream (each call is a
+    C-ABI entry point restricted to one kernel).  Returns {name: ms} and the selection pair count."""
+    from nsa_b200 import _lib
+    L = _lib.lib()
+    B, T, Hq, D = q4.shape
+    Hkv = k4.shape[2]
+    c = CFG
+    scale = D ** -0.5
+    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=q4.device)
+    k3, v3 = k4.view(B * T, Hkv, D), v4.view(B * T, Hkv, D)
+    with torch.no_grad():
+        ck, cv, _ = mod.compressor(k3, v3, cu, None)
+    Tc = ck.shape[1]
+    o_cmp, o_slc, o_swa = (torch.empty_like(q4) for _ in range(3))
+    lse_cmp, lse_slc, lse_swa, delta = (torch.empty(B, T, Hq, dtype=torch.float32, device=q4.device) for _ in range(4))
+    idx = torch.empty(B, T, Hkv, c["n_sel"], dtype=torch.int32, device=q4.device)
+    dq, dk, dv = torch.empty_like(q4), torch.empty_like(k4), torch.empty_like(v4)
+    dck, dcv = torch.empty_like(ck), torch.empty_like(cv)
+    ws1 = torch.empty(L.nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, c["n_sel"], c["sel_block"]), dtype=torch.uint8,
+                      device=q4.device)
+    ws2 = torch.empty(L.nsa_cmp_attn_bwd_workspace_bytes(B, T, Tc, Hkv, D), dtype=torch.uint8, device=q4.device)
+    P, S = _lib.ptr, _lib.stream
+    wk = mod.compressor.compressor_k.weight.detach().permute(2, 1, 0).reshape(c["block"] * D, D).contiguous()
+    bk = mod.compressor.compressor_k.bias.detach()
+    cin = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=q4.device)
+    cout = torch.arange(0, (B + 1) * Tc, Tc, dtype=torch.int32, device=q4.device)
+    dwk = torch.empty(c["block"] * D, D, dtype=torch.float32, device=q4.device)
+    dbk = torch.empty(D, dtype=torch.float32, device=q4.device)
+    ws3 = torch.empty(L.nsa_compress_bwd_workspace_bytes(B, Hkv, D, c["block"]), dtype=torch.uint8, device=q4.device)
+    g1 = torch.full((B, T, Hq), 0.5, dtype=torch.bfloat16, device=q4.device)
+
+    calls = {
+        "compress_fwd(one of k,v)": lambda: L.nsa_compress_fwd(P(k3), P(wk), P(bk), P(ck), P(cin), P(cout), B, Hkv, D,
+                                                                c["block"], c["stride"], Tc, S()),
+        "cmp_attn_fwd+select": lambda: L.nsa_cmp_attn_fwd(P(q4), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, B, T,
+                                                          Tc, Hq, Hkv, D, c["block"], c["stride"], 1, scale, c["n_sel"],
+                                                          5, 4, 0, S()),
+        "sel_fwd": lambda: L.nsa_sel_swa_fwd(P(q4), P(k4), P(v4), P(idx), 0, None, P(o_slc), P(lse_slc), None, None, None,
+                                             None, None, None, None, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"], 0,
+                                             scale, S()),
+        "swa_fwd": lambda: L.nsa_sel_swa_fwd(P(q4), P(k4), P(v4), None, 0, None, None, None, P(o_swa), P(lse_swa), None,
+                                             None, None, None, None, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"],
+                                             c["window"], scale, S()),
+        "combine": lambda: L.nsa_combine(P(o_slc), P(g1), P(o_swa), P(g1), P(o_cmp), P(g1), P(dq), B * T * Hq, D, S()),
+        "rowdot(delta)": lambda: L.nsa_rowdot(P(o_slc), P(do4), None, P(delta), None, B * T * Hq, D, S()),
+        "sel_dq": lambda: L.nsa_sel_swa_bwd(P(q4), P(k4), P(v4), P(idx), 0, None, P(do4), P(lse_slc), P(delta), None, None,
+                                            None, None, None, P(dq), 0, None, None, None, 0, B, T, Hq, Hkv, D, c["n_sel"],
+                                            c["sel_block"], 0, scale, S()),
+        "swa_dq": lambda: L.nsa_sel_swa_bwd(P(q4), P(k4), P(v4), None, 0, None, None, None, None, None, P(do4), P(lse_swa),
+                                            P(delta), None, P(dq), 0, None, None, None, 0, B, T, Hq, Hkv, D, c["n_sel"],
+                                            c["sel_block"], c["window"], scale, S()),
+        "sel+swa_dkv(+reverse index)": lambda: L.nsa_sel_swa_bwd(
+            P(q4), P(k4), P(v4), P(idx), 0, None, P(do4), P(lse_slc), P(delta), None, P(do4), P(lse_swa), P(delta), None,
+            None, 0, P(dk), P(dv), P(ws1), ws1.numel(), B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"], c["window"], scale,
+            S()),
+        "cmp_dq": lambda: L.nsa_cmp_attn_bwd(P(q4), P(ck), P(cv), P(lse_cmp), P(do4), P(delta), None, P(dq), 0, None, None,
+                                             None, 0, B, T, Tc, Hq, Hkv, D, c["block"], c["stride"], 1, scale, S()),
+        "cmp_dkv(+reduce)": lambda: L.nsa_cmp_attn_bwd(P(q4), P(ck), P(cv), P(lse_cmp), P(do4), P(delta), None, None, 0,
+                                                       P(dck), P(dcv), P(ws2), ws2.numel(), B, T, Tc, Hq, Hkv, D,
+                                                       c["block"], c["stride"], 1, scale, S()),
+        "compress_bwd(one of k,v)": lambda: L.nsa_compress_bwd(P(k3), P(wk), P(dck), P(dk), P(dwk), P(dbk), P(ws3),
+                                                                ws3.numel(), P(cin), P(cout), B, Hkv, D, c["block"],
+                                                                c["stride"], T, B * Tc, S()),
+    }
+    out = {}
+    for name, fn in calls.items():
+        _lib.check(fn(), name)           # warm-up, and produces the tensors later calls read
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            _lib.check(fn(), name)
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = e0.elapsed_time(e1) / reps
+    t = torch.arange(T, device=q4.device).view(1, T, 1, 1)
+    valid = (idx >= 0) & (idx.long() * c["sel_block"] <= t)
+    pairs = int(valid.sum().item())               # (token, kv head, block) visits
+    keys_per_seq_head = pairs * c["sel_block"] / (B * Hkv)
+    _lib.device_status()
+    return out, keys_per_seq_head
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import nsa_b200
+    from nsa_b200 import _lib
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    c = CFG
+    if c["B"] % world:
+        raise SystemExit("batch %d does not divide over %d ranks" % (c["B"], world))
+    Bl = c["B"] // world
+    T, Hq, Hkv, D = c["T"], c["Hq"], c["Hkv"], c["D"]
+    gen = torch.Generator().manual_seed(c["seed"] * 1000 + rank)
+    host = {}
+    for name, h in (("q", Hq), ("k", Hkv), ("v", Hkv), ("do", Hq)):
+        host[name] = torch.randn(Bl * T, h, D, generator=gen).to(torch.bfloat16).pin_memory()
+    wgen = torch.Generator().manual_seed(c["seed"])
+    mod = nsa_b200.NSAAttention(D, True, None, 0.0, compression_stride=c["stride"], compression_block=c["block"],
+                                selection_block=c["sel_block"], selected_block_count=c["n_sel"],
+                                sliding_window=c["window"], device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.copy_(torch.randn(p.shape, generator=wgen) * 0.02)
+    params = list(mod.parameters())
+    cu = torch.arange(0, (Bl + 1) * T, T, dtype=torch.int32, device=dev)
+    q, k, v, do = (host[n].to(dev) for n in ("q", "k", "v", "do"))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    out_h = {n: torch.empty_like(host[m]).pin_memory() for n, m in (("o", "q"), ("dq", "q"), ("dk", "k"), ("dv", "v"))}
+
+    def step(qd, kd, vd, dod):
+        for t in [qd, kd, vd] + params:
+            t.grad = None
+        o = mod(qd, kd, vd, cu, T)
+        o.backward(dod)
+        if world > 1:
+            flat = torch.cat([p.grad.reshape(-1) for p in params])
+            dist.all_reduce(flat)
+        return o
+
+    def step_e2e():
+        qd, kd, vd, dod = (host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "do"))
+        qd.requires_grad_(True), kd.requires_grad_(True), vd.requires_grad_(True)
+        o = step(qd, kd, vd, dod)
+        out_h["o"].copy_(o.detach(), non_blocking=True)
+        out_h["dq"].copy_(qd.grad, non_blocking=True)
+        out_h["dk"].copy_(kd.grad, non_blocking=True)
+        out_h["dv"].copy_(vd.grad, non_blocking=True)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.time()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        w1 = time.time()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / steps, w0, w1
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches = [0, 0]
+
+    def counted_step():
+        launches[0] = launches[0] or _lib.lib().nsa_kernel_launch_count()
+        step(q, k, v, do)
+        launches[1] = _lib.lib().nsa_kernel_launch_count()
+
+    for _ in range(args.warmup):
+        step(q, k, v, do)
+    ms_step, w0, w1 = timed(counted_step, args.steps, 0)
+    clocks = sampler.stop(w0, w1) if rank == 0 else None
+    _lib.device_status()
+    ms_e2e, _, _ = timed(step_e2e, max(1, min(args.steps, 5)), 1)
+    _lib.device_status()
+
+    tokens = c["B"] * T
+    line = None
+    if rank == 0:
+        peaks = read_peaks()
+        with torch.no_grad():
+            kern, keys_per = per_kernel_breakdown(torch, nsa_b200, mod, q.detach().view(Bl, T, Hq, D),
+                                                  k.detach().view(Bl, T, Hkv, D), v.detach().view(Bl, T, Hkv, D),
+                                                  do.view(Bl, T, Hq, D))
+        fm_nom = flop_model(c["B"], T, Hq, Hkv, D, c["block"], c["stride"], c["sel_block"], c["n_sel"], c["window"])
+        fm_loc = flop_model(Bl, T, Hq, Hkv, D, c["block"], c["stride"], c["sel_block"], c["n_sel"], c["window"],
+                            nsel_pairs=keys_per)
+        # algorithmic flops per kernel launch (per rank): forward 4D per (row,key); the backward's 10D per (row,key)
+        # is split 4D to the dQ kernel (dQ + half of the S/dP recompute) and 6D to the dK/dV kernel
+        kflops = {
+            "sel_fwd": fm_loc["slc"], "swa_fwd": fm_loc["swa"], "cmp_attn_fwd+select": fm_loc["cmp"],
+            "sel_dq": fm_loc["slc"], "swa_dq": fm_loc["swa"], "cmp_dq": fm_loc["cmp"],
+            "sel+swa_dkv(+reverse index)": 1.5 * (fm_loc["slc"] + fm_loc["swa"]), "cmp_dkv(+reduce)": 1.5 * fm_loc["cmp"],
+            "compress_fwd(one of k,v)": fm_loc["comp"] / 2, "compress_bwd(one of k,v)": fm_loc["comp"],
+        }
+        dom = max((n for n in kern if n in kflops), key=lambda n: kern[n])
+        achieved = kflops[dom] / (kern[dom] * 1e-3) / 1e12
+        peak = peaks["tf_sustained"]
+        roof = {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 2), "peak": peak, "unit": "TFLOP/s",
+                "frac": round(achieved / peak, 4), "peak_source": peaks["source"] + " (sustained bf16 GEMM)",
+                "traffic": None, "ms_per_launch": round(kern[dom], 3),
+                "algorithmic_flops_per_launch": kflops[dom]}
+        cb = None
+        if world == 1 and not args.no_cpu:
+            cb, _ = cpu_step(1024, 1, 0)
+        h2d = sum(host[n].numel() * 2 for n in ("q", "k", "v", "do"))
+        d2h = sum(t.numel() * 2 for t in out_h.values())
+        line = {
+            "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": c["B"], "seq_len": T, "parallelism": "batch-sharded x%d" % world,
+                       "l2": "inputs larger than L2 (q and dO are 1.07 GB each at N=1)",
+                       "selection": "indices produced by the fused top-16 of the step itself (oracle-style scoring)"},
+            "tflops_algorithmic": fm_nom["total"] / (ms_step * 1e-3) / 1e12,
+            "tflops_frac_of_sustained_peak": fm_nom["total"] / (ms_step * 1e-3) / 1e12 / world / peaks["tf_sustained"],
+            "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
+                    "d2h_bytes_per_step": d2h * world, "ms_per_step": ms_e2e},
+            "gpu_launches": int(launches[1] - launches[0]),
+            "roofline": roof, "kernels_ms": {n: round(v, 3) for n, v in kern.items()},
+            "selected_keys_per_seq_kvhead": keys_per, "clocks": clocks, "cpu_baseline": cb,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_profile_case():
+    """B=1 slice of the workload (q, dO 134 MB each: larger than L2, well under 1 GB on the device)."""
+    import torch
+    import nsa_b200
+    c = CFG
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(c["seed"])
+    T, Hq, Hkv, D = c["T"], c["Hq"], c["Hkv"], c["D"]
+    q, k, v, do = (torch.randn(1, T, h, D, generator=gen).to(dev, torch.bfloat16) for h in (Hq, Hkv, Hkv, Hq))
+    mod = nsa_b200.NSAAttention(D, True, None, 0.0, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.copy_(torch.randn(p.shape, generator=gen) * 0.02)
+        kern, keys = per_kernel_breakdown(torch, nsa_b200, mod, q, k, v, do, reps=1)
+    print(json.dumps({"profile_case": "B=1 T=8192 Hq=64 Hkv=4 D=128", "kernels_ms": kern, "selected_keys": keys}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-case", action="store_true",
+                    help="small case for ncu: B=1 of the workload, every kernel family launched twice, no timing loop")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.profile_case:
+        run_profile_case()
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

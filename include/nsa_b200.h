@@ -32,6 +32,8 @@ int nsa_abi_version(void);
 const char* nsa_last_error(void);
 /* Synchronises the current device, returns and clears the device-side error code (0 = none). */
 int nsa_device_status(void);
+/* Number of kernels this library has launched in this process so far (for benchmarks' bookkeeping). */
+long long nsa_kernel_launch_count(void);
 
 /* ---- compression -------------------------------------------------------------------------------
  * Replaces compress_kv / _compress_kv.forward (nsa/compression_kv.py:178-217, kernel :21-57) and the two

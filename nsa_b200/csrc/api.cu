@@ -56,6 +56,8 @@ extern "C" {
 
 int nsa_abi_version(void) { return 1; }
 
+long long nsa_kernel_launch_count(void) { return launch_count(); }
+
 const char* nsa_last_error(void) { return g_err; }
 
 int nsa_device_status(void) {

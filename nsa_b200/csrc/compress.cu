@@ -281,6 +281,7 @@ int fwd(const CompressArgs& a, cudaStream_t s) {
   if (a.max_out <= 0) return 0;
   const dim3 grid((a.max_out + 63) / 64, a.nseq * a.H);
   kern<<<grid, 128, smem, s>>>(a);
+  note_launches(1);
   return (int)cudaGetLastError();
 }
 
@@ -294,7 +295,10 @@ int bwd(const CompressArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return (int)e;
     const int nchunk = (a.max_in + a.d - 1) / a.d;
     const dim3 grid((nchunk + 63) / 64, a.nseq * a.H, a.d);
-    if (a.max_in > 0) kern<<<grid, 128, smem, s>>>(a);
+    if (a.max_in > 0) {
+      kern<<<grid, 128, smem, s>>>(a);
+      note_launches(1);
+    }
   }
   if (a.dw) {
     const int smem = 2 * 2 * 64 * 128 * (D / 64) + 1024;
@@ -305,10 +309,12 @@ int bwd(const CompressArgs& a, cudaStream_t s) {
     kern<<<dim3(a.l, nsplit), D * 2, smem, s>>>(a, nsplit);
     const long long n = (long long)a.l * D * D;
     compress_dw_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a.ws, a.dw, n, nsplit);
+    note_launches(2);
   }
   if (a.dbias) {
     const int nt = 1024 / D * D;
     compress_dbias_kernel<<<1, nt, nt * sizeof(float), s>>>(a.dy, a.dbias, (long long)a.total_out * a.H, D);
+    note_launches(1);
   }
   return (int)cudaGetLastError();
 }

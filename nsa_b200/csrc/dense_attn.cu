@@ -425,6 +425,7 @@ int launch(const DenseArgs& a, cudaStream_t s) {
   const int grid = (int)(total < num_sms() ? total : num_sms());
   if (grid <= 0) return 0;
   kern<<<grid, kThreads, smem, s>>>(tmK, tmV, a, nst, pool_stride_f);
+  note_launches(1);
   return (int)cudaGetLastError();
 }
 

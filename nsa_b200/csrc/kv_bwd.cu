@@ -312,6 +312,7 @@ int launch(const KvArgs& a, cudaStream_t s) {
     return -33;
   }
   kern<<<(unsigned)grid, kThreads, smem, s>>>(tmQ, tmA, tmB, tmK, tmV, a, nst);
+  note_launches(1);
   return (int)cudaGetLastError();
 }
 

@@ -205,6 +205,7 @@ int launch_rowdot(const bf16* o, const bf16* dout, const bf16* gate, float* delt
     set_error("head_dim %d not supported (64 or 128)", D);
     return -2;
   }
+  note_launches(1);
   return (int)cudaGetLastError();
 }
 
@@ -217,6 +218,7 @@ int launch_combine(const bf16* a0, const bf16* g0, const bf16* a1, const bf16* g
   }
   const long long n8 = rows * (D / 8);
   combine_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, s>>>(a0, g0, a1, g1, a2, g2, o, n8, D / 8);
+  note_launches(1);
   return (int)cudaGetLastError();
 }
 
@@ -236,6 +238,7 @@ int launch_build_rev(const RevArgs& a, cudaStream_t s) {
   rev_hist_kernel<<<grid, 128, sm, s>>>(a);
   rev_scan_kernel<<<a.B * a.H, 256, sm, s>>>(a);
   rev_fill_kernel<<<grid, 32, sm, s>>>(a);
+  note_launches(3);
   return (int)cudaGetLastError();
 }
 
@@ -245,6 +248,7 @@ int launch_reduce_segments(const float* part, bf16* out, int nseg, long long n_p
   const long long pairs = n_per_seg / 2;
   reduce_segments_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(part, out, nseg, n_per_seg, T, Lk, Hk * D,
                                                                           seg_len, cblock, cstride, causal);
+  note_launches(1);
   return (int)cudaGetLastError();
 }
 

@@ -63,30 +63,63 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == kConsumerWarps) {
     // ------------------------------- producer ------------------------------------------------
-    if (lane != 0) return;
+    // All 32 lanes fetch the item's block indices at once (one round trip instead of one per block); lane 0
+    // then waits for a free stage and issues the TMA gathers.
     uint32_t it = 0;
+    // the first 32 indices of the next item are fetched while the current item's gathers are issued
+    auto item_row = [&](long long item) {
+      const int hg = (int)(item % HG);
+      const int t = a.T - 1 - (int)((item / HG) % a.T);
+      const int b = (int)(item / ((long long)HG * a.T));
+      return ((long long)b * a.T + t) * a.Hkv + hg / G16;
+    };
+    auto fetch = [&](long long item, int& cnt, int& first) {
+      cnt = 0;
+      first = -1;
+      if (item >= total) return;
+      const long long row = item_row(item);
+      cnt = a.S;
+      if (a.counts) cnt = min(cnt, a.counts[row]);
+      if (lane < cnt) first = load_block_index(a.idx, a.idx64, row * a.S + lane, BS);
+    };
+    int cnt_next, first_next;
+    fetch(blockIdx.x, cnt_next, first_next);
     for (long long item = blockIdx.x; item < total; item += gridDim.x) {
       const int hg = (int)(item % HG);
       const int t = a.T - 1 - (int)((item / HG) % a.T);
       const int b = (int)(item / ((long long)HG * a.T));
       const int hkv = hg / G16;
       const long long row = ((long long)b * a.T + t) * a.Hkv + hkv;
-      int cnt = a.S;
-      if (a.counts) cnt = min(cnt, a.counts[row]);
-      for (int s = 0; s < cnt; ++s) {
-        const int blk = load_block_index(a.idx, a.idx64, row * a.S + s, BS);
-        if (blk < 0 || (long long)blk * BS > t) continue;
-        const int stage = it % nst;
-        const uint32_t ph = (it / nst) & 1;
-        if (!mbar_wait(empty_bar(stage), ph ^ 1, DEV_ERR_EMPTY_WAIT)) return;
-        mbar_expect_tx(full_bar(stage), stage_bytes);
-        const uint32_t dst = sbase + stage * stage_bytes;
+      const int cnt = cnt_next, first = first_next;
+      fetch(item + gridDim.x, cnt_next, first_next);
+      for (int s0 = 0; s0 < cnt; s0 += 32) {
+        const int mine = (s0 == 0) ? first
+                                   : ((s0 + lane < cnt) ? load_block_index(a.idx, a.idx64, row * a.S + s0 + lane, BS) : -1);
+        const unsigned valid = __ballot_sync(0xffffffffu, mine >= 0 && (long long)mine * BS <= t);
+        // lanes take turns handing their block to lane 0 (warp-uniform loop over the set bits)
+        unsigned rem = valid;
+        while (rem) {
+          const int j = __ffs(rem) - 1;
+          rem &= rem - 1;
+          const int blk = __shfl_sync(0xffffffffu, mine, j);
+          int good = 1;
+          if (lane == 0) {
+            const int stage = it % nst;
+            const uint32_t ph = (it / nst) & 1;
+            good = mbar_wait(empty_bar(stage), ph ^ 1, DEV_ERR_EMPTY_WAIT) ? 1 : 0;
+            if (good) {
+              mbar_expect_tx(full_bar(stage), stage_bytes);
+              const uint32_t dst = sbase + stage * stage_bytes;
 #pragma unroll
-        for (int p = 0; p < D / 64; ++p) {
-          tma_load_4d(dst + p * panel_bytes, &tmK, full_bar(stage), p * 64, hkv, blk * BS, b);
-          tma_load_4d(dst + tile_bytes + p * panel_bytes, &tmV, full_bar(stage), p * 64, hkv, blk * BS, b);
+              for (int p = 0; p < D / 64; ++p) {
+                tma_load_4d(dst + p * panel_bytes, &tmK, full_bar(stage), p * 64, hkv, blk * BS, b);
+                tma_load_4d(dst + tile_bytes + p * panel_bytes, &tmV, full_bar(stage), p * 64, hkv, blk * BS, b);
+              }
+            }
+          }
+          if (!__shfl_sync(0xffffffffu, good, 0)) return;
+          ++it;
         }
-        ++it;
       }
     }
     return;
@@ -299,6 +332,7 @@ int launch(const SelArgs& a, cudaStream_t s) {
   const int grid = (int)(total < num_sms() ? total : num_sms());
   if (grid <= 0) return 0;
   kern<<<grid, kThreads, smem, s>>>(tmK, tmV, a, nst);
+  note_launches(1);
   return (int)cudaGetLastError();
 }
 

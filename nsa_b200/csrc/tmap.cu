@@ -1,9 +1,14 @@
 #include "tmap.h"
 
 #include <cudaTypedefs.h>
+#include <atomic>
 #include <mutex>
 
 namespace nsa {
+
+static std::atomic<long long> g_launches{0};
+void note_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 static std::once_flag g_once;

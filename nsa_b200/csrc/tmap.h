@@ -16,4 +16,8 @@ int make_tmap_rows2d(CUtensorMap* out, const void* base, int D, long long rows, 
 
 void set_error(const char* fmt, ...);
 
+// Process-wide count of kernels this library has launched (read through nsa_kernel_launch_count()).
+void note_launches(int n);
+long long launch_count();
+
 }  // namespace nsa

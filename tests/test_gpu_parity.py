@@ -30,10 +30,18 @@ def _dev(x):
     return x.to(DEV, torch.bfloat16)
 
 
-def _close(name, got, ref, atol=ATOL, rtol=RTOL):
+def _close(name, got, ref, atol=ATOL, rtol=RTOL, scaled=False):
+    """|got - ref| <= atol + rtol*|ref| elementwise.  With ``scaled`` (gradients that are sums over thousands of
+    (token, head) rows: dK, dV, dCK, dCV, weight gradients) every row (last dimension) of both sides is first divided
+    by max(1, RMS of the reference row): the bf16 rounding of the P and dS operands (the same roundings the
+    reference's kernels make) gives an error proportional to the energy summed into the row, not to the value of
+    the single element, so the absolute term is read on the unit-RMS row."""
     got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
     assert got.shape == ref.shape, "%s: shape %s vs %s" % (name, tuple(got.shape), tuple(ref.shape))
     assert not torch.isnan(got).any(), "%s: NaN in kernel output" % name
+    if scaled:
+        s = ref.square().mean(-1, keepdim=True).sqrt().clamp_min(1.0)
+        got, ref = got / s, ref / s
     err = (got - ref).abs()
     bad = err > atol + rtol * ref.abs()
     assert not bad.any(), "%s: %d/%d outside tolerance, max abs err %.4g (ref max %.4g)" % (
@@ -66,8 +74,8 @@ def test_cmp_attention_golden(nsa, name):
     assert hard == 0, "%d rows select a block outside the 1e-3 waiver (%d rows differ at all)" % (hard, soft)
     o.backward(_dev(c["do"]))
     _close("dq", q.grad, g["dq"])
-    _close("dck", ck.grad, g["dck"])
-    _close("dcv", cv.grad, g["dcv"])
+    _close("dck", ck.grad, g["dck"], scaled=True)
+    _close("dcv", cv.grad, g["dcv"], scaled=True)
     nsa._lib.device_status()
 
 
@@ -81,9 +89,9 @@ def test_selection_golden(nsa, name):
     if c["window"] > 0:
         o.backward(_dev(c["do"]))
         _close("dq", q.grad, g["dq"])
-        _close("dk", k.grad, g["dk"])
+        _close("dk", k.grad, g["dk"], scaled=True)
         ok = ~torch.isnan(g["dv"])          # the reference's dv holds NaN at keys of its empty-selection rows
-        _close("dv", torch.where(ok, v.grad.float().cpu(), torch.zeros(())), torch.nan_to_num(g["dv"], nan=0.0))
+        _close("dv", torch.where(ok, v.grad.float().cpu(), torch.zeros(())), torch.nan_to_num(g["dv"], nan=0.0), scaled=True)
     nsa._lib.device_status()
 
 
@@ -101,8 +109,8 @@ def test_compression_golden(nsa, name):
     tgt = torch.sin(torch.arange(ck.numel(), dtype=torch.float32)).reshape(ck.shape)
     ck.backward(_dev(tgt))
     # the kernel sees the bf16-rounded upstream gradient; the golden used the fp32 one
-    _close("dx", x.grad, g["dx"], atol=3e-2)
-    _close("dw", w.grad, g["dw"], atol=6e-2, rtol=2e-2)
+    _close("dx", x.grad, g["dx"], scaled=True)
+    _close("dw", w.grad, g["dw"], scaled=True)
     comp = nsa.compression_kv.KVCompressor(c["stride"], c["block"], x.shape[-1], DEV, torch.bfloat16)
     with torch.no_grad():
         comp.compressor_k.weight.copy_(c["conv_w"])
@@ -160,8 +168,8 @@ def test_selection_and_window_fwd_bwd(nsa, D, BS, S, Hq, Hkv, T, window):
     loss_k.backward()
     loss_o.backward()
     _close("dq", qd.grad, qo.grad)
-    _close("dk", kd.grad, ko.grad)
-    _close("dv", vd.grad, vo.grad)
+    _close("dk", kd.grad, ko.grad, scaled=True)
+    _close("dv", vd.grad, vo.grad, scaled=True)
     nsa._lib.device_status()
 
 
@@ -186,8 +194,8 @@ def test_cmp_attention_fwd_bwd(nsa, D, Hq, Hkv, T, block, stride):
     o.backward(_dev(do))
     (ro * do).sum().backward()
     _close("dq", qd.grad, qo.grad)
-    _close("dck", kd.grad, ko.grad)
-    _close("dcv", vd.grad, vo.grad)
+    _close("dck", kd.grad, ko.grad, scaled=True)
+    _close("dcv", vd.grad, vo.grad, scaled=True)
     # the reference's repeated-head calling convention gives the same result
     o2, idx2 = nsa.triton_attention.flash_attn_func(_dev(q), _dev(ck).repeat_interleave(Hq // Hkv, 2),
                                                     _dev(cv).repeat_interleave(Hq // Hkv, 2), stride, block, True, None,
@@ -241,7 +249,7 @@ def test_compression_varlen_fwd_bwd(nsa, D, H, block, stride, lens):
     ck.backward(_dev(dy))
     (ry * dy).sum().backward()
     _close("dx", xd.grad, xo.grad)
-    _close("dw", wd.grad, wo.grad, atol=5e-2, rtol=2e-2)
+    _close("dw", wd.grad, wo.grad, scaled=True)
     nsa._lib.device_status()
 
 
@@ -303,16 +311,21 @@ def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window):
     o_swa, _ = O.sliding_window_attention(qo, ko, vo, window)
     gate = qo @ wg_o.t() + bg_o
     ref = o_slc * gate[..., 0:1] + o_swa * gate[..., 1:2] + o_cmp * gate[..., 2:3]
-    _close("module output", out.view(B, T, Hq, D), ref, atol=3e-2)
+    _close("module output", out.view(B, T, Hq, D), ref)
     do = _r(torch.randn(B, T, Hq, D, generator=gen))
     out.backward(_dev(do.reshape(B * T, Hq, D)))
     (ref * do).sum().backward()
-    _close("dq", qd.grad.view(B, T, Hq, D), qo.grad, atol=4e-2, rtol=2e-2)
-    _close("dk", kd.grad.view(B, T, Hkv, D), ko.grad, atol=4e-2, rtol=2e-2)
-    _close("dv", vd.grad.view(B, T, Hkv, D), vo.grad, atol=4e-2, rtol=2e-2)
-    _close("d gating.weight", mod.gating.weight.grad, wg_o.grad, atol=0.5, rtol=3e-2)
-    _close("d conv_k.weight", mod.compressor.compressor_k.weight.grad, wk_o.grad, atol=0.5, rtol=5e-2)
-    _close("d conv_v.bias", mod.compressor.compressor_v.bias.grad, bv_o.grad, atol=0.5, rtol=5e-2)
+    # dq is the bf16 sum of four bf16 branch gradients (selected, window, compressed, gate), as in the reference's
+    # autograd graph: three extra roundings, so 3e-2 on the unit-RMS row
+    _close("dq", qd.grad.view(B, T, Hq, D), qo.grad, atol=3e-2, scaled=True)
+    _close("dk", kd.grad.view(B, T, Hkv, D), ko.grad, atol=3e-2, scaled=True)
+    _close("dv", vd.grad.view(B, T, Hkv, D), vo.grad, scaled=True)
+    _close("d gating.weight", mod.gating.weight.grad, wg_o.grad, scaled=True)
+    _close("d gating.bias", mod.gating.bias.grad, bg_o.grad, scaled=True)
+    _close("d conv_k.weight", mod.compressor.compressor_k.weight.grad, wk_o.grad, scaled=True)
+    _close("d conv_v.weight", mod.compressor.compressor_v.weight.grad, wv_o.grad, scaled=True)
+    _close("d conv_k.bias", mod.compressor.compressor_k.bias.grad, bk_o.grad, scaled=True)
+    _close("d conv_v.bias", mod.compressor.compressor_v.bias.grad, bv_o.grad, scaled=True)
     nsa._lib.device_status()
 
 
