@@ -117,6 +117,33 @@ __device__ __forceinline__ void mma_a_b(float (&acc)[D / 8][4], const uint32_t (
   }
 }
 
+// Same as mma_a_bt<D,16> but with the contraction split over two accumulator sets (even / odd k-steps): four
+// independent mma chains instead of two, which halves the exposed tensor-pipe latency when a warp has no
+// other work to overlap.
+template <int D>
+__device__ __forceinline__ void mma_a_bt16_split(float (&acc)[2][4], const uint32_t (&af)[D / 16][4], uint32_t base,
+                                                 uint32_t panel_bytes, int row0, int lane) {
+  const int m = lane >> 3, rr = lane & 7;
+  const int row = row0 + (m >> 1) * 8 + rr;
+  float odd[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) odd[i][0] = odd[i][1] = odd[i][2] = odd[i][3] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ks += 2) {
+    uint32_t b0, b1, b2, b3, c0, c1, c2, c3;
+    ldsm_x4(tile_addr(base, panel_bytes, row, ks * 2 + (m & 1)), b0, b1, b2, b3);
+    ldsm_x4(tile_addr(base, panel_bytes, row, ks * 2 + 2 + (m & 1)), c0, c1, c2, c3);
+    mma_bf16(acc[0], af[ks], b0, b1);
+    mma_bf16(acc[1], af[ks], b2, b3);
+    mma_bf16(odd[0], af[ks + 1], c0, c1);
+    mma_bf16(odd[1], af[ks + 1], c2, c3);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[i][c] += odd[i][c];
+}
+
 // Load the A-fragments of 16 rows [row0, row0+16) x D of a swizzled shared tile.
 template <int D>
 __device__ __forceinline__ void load_a_frags(uint32_t (&af)[D / 16][4], uint32_t base, uint32_t panel_bytes,

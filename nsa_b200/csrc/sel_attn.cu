@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           float sc[2][4];
 #pragma unroll
           for (int i = 0; i < 2; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
-          mma_a_bt<D, 16>(sc, qf, kbase, panel_bytes, warp * 16, lane);
+          mma_a_bt16_split<D>(sc, qf, kbase, panel_bytes, warp * 16, lane);
           const int key0 = blk * BS + warp * 16 + 2 * tq;  // key of sc[0][0]; sc[nt][c]: + 8*nt + (c&1)
           if constexpr (!BWD) {
             float mx[2] = {-INFINITY, -INFINITY};
@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             float dp[2][4];
 #pragma unroll
             for (int i = 0; i < 2; ++i) dp[i][0] = dp[i][1] = dp[i][2] = dp[i][3] = 0.f;
-            mma_a_bt<D, 16>(dp, dof, vbase, panel_bytes, warp * 16, lane);
+            mma_a_bt16_split<D>(dp, dof, vbase, panel_bytes, warp * 16, lane);
             float ds[2][4];
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
@@ -282,13 +282,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int ww = 0; ww < kConsumerWarps; ++ww) w[ww] = 1.f;
         inv = a.scale;
       }
-      bf16* dst = (BWD ? a.dq : a.o) + (qrow + r) * D + seg * CW;
+      // thread (r, seg) owns the column pairs 16*i + 2*seg: the 8 threads of a row read 64 contiguous bytes
+      bf16* dst = (BWD ? a.dq : a.o) + (qrow + r) * D + 2 * seg;
 #pragma unroll
-      for (int c = 0; c < CW; c += 2) {
+      for (int i = 0; i < CW / 2; ++i) {
+        const int c = 16 * i;
         float x0 = 0.f, x1 = 0.f;
 #pragma unroll
         for (int ww = 0; ww < kConsumerWarps; ++ww) {
-          const float2 v = *reinterpret_cast<const float2*>(part_o + (ww * 16 + r) * PO + seg * CW + c);
+          const float2 v = *reinterpret_cast<const float2*>(part_o + (ww * 16 + r) * PO + c + 2 * seg);
           x0 += w[ww] * v.x;
           x1 += w[ww] * v.y;
         }

@@ -304,6 +304,7 @@ def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window):
     wk_o, bk_o, wv_o, bv_o = (t.clone().requires_grad_(True) for t in (wk, bk, wv, bv))
     ck_o = O.compress_conv(ko, wk_o, bk_o, 32, 16)
     cv_o = O.compress_conv(vo, wv_o, bv_o, 32, 16)
+    ck_o.retain_grad()
     wg_o = mod.gating.weight.detach().float().cpu().requires_grad_(True)
     bg_o = mod.gating.bias.detach().float().cpu().requires_grad_(True)
     o_cmp, _ = O.cmp_attention(qo, ck_o, cv_o, 16, 32, True)
@@ -320,12 +321,23 @@ def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window):
     _close("dq", qd.grad.view(B, T, Hq, D), qo.grad, atol=3e-2, scaled=True)
     _close("dk", kd.grad.view(B, T, Hkv, D), ko.grad, atol=3e-2, scaled=True)
     _close("dv", vd.grad.view(B, T, Hkv, D), vo.grad, scaled=True)
-    _close("d gating.weight", mod.gating.weight.grad, wg_o.grad, scaled=True)
-    _close("d gating.bias", mod.gating.bias.grad, bg_o.grad, scaled=True)
-    _close("d conv_k.weight", mod.compressor.compressor_k.weight.grad, wk_o.grad, scaled=True)
-    _close("d conv_v.weight", mod.compressor.compressor_v.weight.grad, wv_o.grad, scaled=True)
-    _close("d conv_k.bias", mod.compressor.compressor_k.bias.grad, bk_o.grad, scaled=True)
-    _close("d conv_v.bias", mod.compressor.compressor_v.bias.grad, bv_o.grad, scaled=True)
+    # parameter gradients sit behind two bf16-rounded gradient stages (branch gradient, then the compression or
+    # gate backward summed over every token): 4e-2 on the unit-RMS row
+    for name, got, ref_g in (("gating.weight", mod.gating.weight.grad, wg_o.grad),
+                             ("gating.bias", mod.gating.bias.grad, bg_o.grad),
+                             ("compressor_k.weight", mod.compressor.compressor_k.weight.grad, wk_o.grad),
+                             ("compressor_v.weight", mod.compressor.compressor_v.weight.grad, wv_o.grad),
+                             ("compressor_v.bias", mod.compressor.compressor_v.bias.grad, bv_o.grad)):
+        _close("d " + name, got, ref_g, atol=4e-2, scaled=True)
+    # The key-side bias gradient is exactly zero in exact arithmetic (a constant added to every compressed key shifts
+    # each score row by a constant); the kernel's value is the sum over B*Tc*Hkv rows of bf16-rounded dCK entries, so it
+    # is bounded by that rounding noise: 2^-8 * sqrt(rows) * RMS(dCK).
+    assert bk_o.grad.abs().max() < 1e-3
+    rows = ck_o.grad.numel() // D
+    noise = 2.0 ** -8 * rows ** 0.5 * float(ck_o.grad.square().mean().sqrt())
+    got = mod.compressor.compressor_k.bias.grad.float().cpu()
+    assert got.abs().max() < 4 * noise, "d compressor_k.bias %.3g exceeds the rounding bound %.3g" % (
+        float(got.abs().max()), 4 * noise)
     nsa._lib.device_status()
 
 
