@@ -51,6 +51,17 @@ int nsa_compress_bwd(const void* x, const void* w, const void* dy, void* dx, flo
                      size_t ws_bytes, const int32_t* cu_in, const int32_t* cu_out, int nseq, int H, int D,
                      int block, int stride, int max_in, int total_out, void* stream);
 size_t nsa_compress_bwd_workspace_bytes(int nseq, int H, int D, int block);
+/* No counterpart in the reference.  The same backward as nsa_compress_bwd for callers that must not allocate
+ * device memory when they need it (a runtime that has already handed out all of its HBM, a plugin host that owns
+ * the allocator): the fp32 partials of the dW reduction go to a 16 MiB device array built into the library, so
+ * there is no workspace argument and the call itself never allocates.  Limit: block*D*D <= 4 Mi floats (for
+ * D = 128 that is block <= 256); larger shapes are rejected with a negative code and must use nsa_compress_bwd.
+ * The first call on a device looks up the array's device address; make that call before any stream capture.
+ * All calls share the one array and leave their partials in it (each call overwrites what it uses, nothing has
+ * to be cleared), so two calls whose kernels could overlap on the GPU (different streams) race: serialise them. */
+int nsa_compress_bwd_noalloc(const void* x, const void* w, const void* dy, void* dx, float* dw, float* dbias,
+                             const int32_t* cu_in, const int32_t* cu_out, int nseq, int H, int D, int block,
+                             int stride, int max_in, int total_out, void* stream);
 
 /* ---- compressed attention + block selection ------------------------------------------------------
  * Replaces _attention.forward (nsa/triton_attention.py:421-476: _attn_fwd, softmax_kernel, group sum,

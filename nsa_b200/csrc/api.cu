@@ -117,6 +117,25 @@ int nsa_compress_bwd(const void* x, const void* w, const void* dy, void* dx, flo
   return launch_compress_bwd(a, (cudaStream_t)stream);
 }
 
+int nsa_compress_bwd_noalloc(const void* x, const void* w, const void* dy, void* dx, float* dw, float* dbias,
+                             const int32_t* cu_in, const int32_t* cu_out, int nseq, int H, int D, int block, int stride,
+                             int max_in, int total_out, void* stream) {
+  if (!x || !w || !dy || !cu_in || !cu_out) return fail(-1, "nsa_compress_bwd_noalloc: null pointer");
+  if (nseq <= 0 || H <= 0) return fail(-1, "nsa_compress_bwd_noalloc: empty shape");
+  if (D != 64 && D != 128) return fail(-2, "nsa_compress_bwd_noalloc: head_dim %d not supported (64 or 128)", D);
+  if (stride <= 0 || block <= 0 || block % stride)
+    return fail(-4, "nsa_compress_bwd_noalloc: block must be a multiple of stride");
+  if (dw && (long long)block * D * D > compress_static_scratch_floats())
+    return fail(-41, "nsa_compress_bwd_noalloc: block*D*D = %lld floats exceeds the built-in scratch of %lld floats; "
+                     "use nsa_compress_bwd with a caller workspace", (long long)block * D * D,
+                compress_static_scratch_floats());
+  CompressArgs a = {};
+  a.x = (const bf16*)x; a.w = (const bf16*)w; a.dy = (const bf16*)dy; a.dx = (bf16*)dx; a.dw = dw; a.dbias = dbias;
+  a.cu_in = cu_in; a.cu_out = cu_out; a.nseq = nseq; a.H = H; a.D = D; a.l = block; a.d = stride;
+  a.max_in = max_in; a.total_out = total_out;
+  return launch_compress_bwd_static(a, (cudaStream_t)stream);
+}
+
 // ---- compressed attention ---------------------------------------------------------------------------
 int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
                      float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,

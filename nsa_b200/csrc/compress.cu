@@ -10,6 +10,8 @@
 //   * dW: split over (sequence, head) into fp32 partials that a second kernel adds in a fixed order.
 //
 // These three GEMMs are 0.1 TFLOP of the 13 TFLOP step; they run on mma.sync tiles fed by cp.async double buffering.
+#include <mutex>
+
 #include "kernels.h"
 #include "tmap.h"
 
@@ -319,6 +321,89 @@ int bwd(const CompressArgs& a, cudaStream_t s) {
   return (int)cudaGetLastError();
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free weight-gradient path.
+//
+// Some hosts of this library may not allocate device memory at the point where they need the compression
+// backward: an inference/training runtime that hands out all of its HBM at start-up and forbids cudaMalloc
+// afterwards, or a plugin sandbox whose allocator the library must not touch.  For them the fp32 partials of the
+// dW reduction live in this fixed array instead of a caller workspace.  Every GPU that loads the library holds the
+// 16 MiB until the process exits.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr long long kStaticScratchFloats = 4ll * 1024 * 1024;   // 16 MiB
+static __device__ __align__(256) float g_dw_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_scratch_ptr[kMaxDevices] = {};
+static std::mutex g_scratch_mutex;
+
+// Device address of g_dw_scratch on the current device.  In host code the symbol's name is only a handle, so the
+// address is queried once per device (with that device current) and cached.
+static int static_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error("device ordinal %d outside the supported range", dev);
+    return -40;
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_dw_scratch);
+    if (e != cudaSuccess) {
+      set_error("cudaGetSymbolAddress for the static scratch failed: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    g_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_scratch_ptr[dev];
+  return 0;
+}
+
+template <int D>
+int bwd_static(const CompressArgs& a0, cudaStream_t s) {
+  CompressArgs a = a0;
+  cudaError_t e;
+  if (a.dx) {
+    const int smem = 2 * (64 * 128 + D * 128) + 1024;
+    auto kern = compress_dx_kernel<D>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    const int nchunk = (a.max_in + a.d - 1) / a.d;
+    const dim3 grid((nchunk + 63) / 64, a.nseq * a.H, a.d);
+    if (a.max_in > 0) {
+      kern<<<grid, 128, smem, s>>>(a);
+      note_launches(1);
+    }
+  }
+  if (a.dw) {
+    const long long per_split = (long long)a.l * D * D;
+    long long nsplit = kStaticScratchFloats / per_split;          // >= 1, checked by the caller
+    if (nsplit > (long long)a.nseq * a.H) nsplit = (long long)a.nseq * a.H;
+    if (nsplit > kDwSplit) nsplit = kDwSplit;
+    float* scratch = nullptr;
+    const int rc = static_scratch(&scratch);
+    if (rc) return rc;
+    a.ws = scratch;
+    const int smem = 2 * 2 * 64 * 128 * (D / 64) + 1024;
+    auto kern = compress_dw_kernel<D>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    // every (j, split) CTA overwrites its whole [D x D] partial, so nothing in the array needs clearing
+    kern<<<dim3(a.l, (unsigned)nsplit), D * 2, smem, s>>>(a, (int)nsplit);
+    compress_dw_reduce_kernel<<<(unsigned)((per_split + 255) / 256), 256, 0, s>>>(a.ws, a.dw, per_split, (int)nsplit);
+    note_launches(2);
+  }
+  if (a.dbias) {
+    const int nt = 1024 / D * D;
+    compress_dbias_kernel<<<1, nt, nt * sizeof(float), s>>>(a.dy, a.dbias, (long long)a.total_out * a.H, D);
+    note_launches(1);
+  }
+  return (int)cudaGetLastError();
+}
+
 }  // namespace
 
 int launch_compress_fwd(const CompressArgs& a, cudaStream_t s) {
@@ -330,6 +415,13 @@ int launch_compress_fwd(const CompressArgs& a, cudaStream_t s) {
 int launch_compress_bwd(const CompressArgs& a, cudaStream_t s) {
   if (a.D == 128) return bwd<128>(a, s);
   if (a.D == 64) return bwd<64>(a, s);
+  set_error("head_dim %d not supported (64 or 128)", a.D);
+  return -2;
+}
+long long compress_static_scratch_floats() { return kStaticScratchFloats; }
+int launch_compress_bwd_static(const CompressArgs& a, cudaStream_t s) {
+  if (a.D == 128) return bwd_static<128>(a, s);
+  if (a.D == 64) return bwd_static<64>(a, s);
   set_error("head_dim %d not supported (64 or 128)", a.D);
   return -2;
 }

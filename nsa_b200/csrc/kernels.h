@@ -104,6 +104,9 @@ struct CompressArgs {
 int launch_compress_fwd(const CompressArgs& a, cudaStream_t s);
 int launch_compress_bwd(const CompressArgs& a, cudaStream_t s);
 int compress_status(int* out);
+// dW partials in the library's fixed device array instead of a caller workspace
+int launch_compress_bwd_static(const CompressArgs& a, cudaStream_t s);
+long long compress_static_scratch_floats();
 
 // ---- small helpers ----------------------------------------------------------------------------
 // delta[r] = (gate ? gate[r] : 1) * sum_d o[r,d]*dout[r,d];  dgate[r] = sum_d o[r,d]*dout[r,d]
