@@ -192,8 +192,8 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
     g1 = torch.full((B, T, Hq), 0.5, dtype=torch.bfloat16, device=q4.device)
 
     calls = {
-        "compress_fwd(one of k,v)": lambda: L.nsa_compress_fwd(P(k3), P(wk), P(bk), P(ck), P(cin), P(cout), B, Hkv, D,
-                                                                c["block"], c["stride"], Tc, S()),
+        "compress_fwd(one of k,v)": lambda: L.nsa_compress_fwd_uniform(P(k3), P(wk), P(bk), P(ck), B, T, Hkv, D, c["block"],
+                                                                        c["stride"], S()),
         "cmp_attn_fwd+select": lambda: L.nsa_cmp_attn_fwd(P(q4), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, B, T,
                                                           Tc, Hq, Hkv, D, c["block"], c["stride"], 1, scale, c["n_sel"],
                                                           5, 4, 0, S()),

@@ -44,6 +44,11 @@ long long nsa_kernel_launch_count(void);
 int nsa_compress_fwd(const void* x, const void* w, const void* bias, void* y, const int32_t* cu_in,
                      const int32_t* cu_out, int nseq, int H, int D, int block, int stride, int max_out,
                      void* stream);
+/* The same forward for B equal-length sequences (x [B*T,H,D], T a multiple of stride): one tcgen05 GEMM per
+ * (batch, head, 128 output rows) whose A tiles are TMA boxes over the overlapping windows; y [B,Tc,H,D] with
+ * Tc = (T-block)/stride + 1 (the Conv1d rule of nsa/compression_kv.py:298-307). */
+int nsa_compress_fwd_uniform(const void* x, const void* w, const void* bias, void* y, int B, int T, int H, int D,
+                             int block, int stride, void* stream);
 /* Replaces _compress_kv.backward (nsa/compression_kv.py:219-266, kernels :62-171) and the Conv1d backward.
  * dy [out_tok,H,D] -> dx [tok,H,D] bf16 (NULL to skip), dw [block*D, D] fp32 (NULL to skip),
  * dbias [D] fp32 (NULL to skip).  ws: nsa_compress_bwd_workspace_bytes() bytes, needed when dw != NULL. */

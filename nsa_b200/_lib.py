@@ -21,6 +21,7 @@ SIGNATURES = {
     "nsa_device_status": (I, []),
     "nsa_kernel_launch_count": (L, []),
     "nsa_compress_fwd": (I, [P, P, P, P, P, P, I, I, I, I, I, I, P]),
+    "nsa_compress_fwd_uniform": (I, [P, P, P, P, I, I, I, I, I, I, P]),
     "nsa_compress_bwd": (I, [P, P, P, P, P, P, P, Z, P, P, I, I, I, I, I, I, I, P]),
     "nsa_compress_bwd_workspace_bytes": (Z, [I, I, I, I]),
     "nsa_compress_bwd_noalloc": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),

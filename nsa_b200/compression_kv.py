@@ -49,7 +49,14 @@ class _CompressOne(torch.autograd.Function):
         max_in = max([cu_in[i + 1] - cu_in[i] for i in range(nseq)] + [0])
         y = torch.empty(total_out, H, D, dtype=torch.bfloat16, device=x.device)
         cin, cout = _cu_tensor(cu_in, x.device), _cu_tensor(cu_out, x.device)
-        if total_out > 0:
+        lens = [cu_in[i + 1] - cu_in[i] for i in range(nseq)]
+        uniform = (nseq > 0 and len(set(lens)) == 1 and lens[0] >= block and lens[0] % stride == 0
+                   and cu_out[1] - cu_out[0] == (lens[0] - block) // stride + 1)
+        if total_out > 0 and uniform:
+            _lib.check(_lib.lib().nsa_compress_fwd_uniform(_lib.ptr(x), _lib.ptr(w), _lib.ptr(bias), _lib.ptr(y), nseq,
+                                                           lens[0], H, D, block, stride, _lib.stream()),
+                       "nsa_compress_fwd_uniform")
+        elif total_out > 0:
             _lib.check(_lib.lib().nsa_compress_fwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(bias), _lib.ptr(y), _lib.ptr(cin),
                                                    _lib.ptr(cout), nseq, H, D, block, stride, max_out, _lib.stream()),
                        "nsa_compress_fwd")

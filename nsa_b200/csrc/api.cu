@@ -64,7 +64,7 @@ int nsa_device_status(void) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(1000 + (int)e, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
   int worst = 0, v = 0;
-  int (*fns[])(int*) = {sel_status, dense_status, kv_status, compress_status, misc_status};
+  int (*fns[])(int*) = {sel_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status};
   for (auto f : fns) {
     v = 0;
     const int rc = f(&v);
@@ -95,6 +95,17 @@ int nsa_compress_fwd(const void* x, const void* w, const void* bias, void* y, co
   a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = (const bf16*)bias; a.y = (bf16*)y;
   a.cu_in = cu_in; a.cu_out = cu_out; a.nseq = nseq; a.H = H; a.D = D; a.l = block; a.d = stride; a.max_out = max_out;
   return launch_compress_fwd(a, (cudaStream_t)stream);
+}
+
+int nsa_compress_fwd_uniform(const void* x, const void* w, const void* bias, void* y, int B, int T, int H, int D,
+                             int block, int stride, void* stream) {
+  if (!x || !w || !y) return fail(-1, "nsa_compress_fwd_uniform: null pointer");
+  if (B <= 0 || H <= 0) return fail(-1, "nsa_compress_fwd_uniform: empty shape");
+  if (stride <= 0 || block <= 0 || block % stride) return fail(-4, "nsa_compress_fwd_uniform: block must be a multiple of stride");
+  if (T < block || T % stride) return fail(-10, "nsa_compress_fwd_uniform: T must be a multiple of stride and at least block");
+  if (stride > 256) return fail(-10, "nsa_compress_fwd_uniform: stride too large for a TMA box");
+  return launch_compress_fwd_uniform((const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)y, B, T, H, D, block, stride,
+                                     (cudaStream_t)stream);
 }
 
 size_t nsa_compress_bwd_workspace_bytes(int nseq, int H, int D, int block) {
@@ -193,7 +204,7 @@ int nsa_cmp_attn_bwd(const void* q, const void* ck, const void* cv, const float*
     a.part = (float*)ws; a.nseg = cmp_segments(T, &a.seg_len);
     a.B = B; a.T = T; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.BS = 64; a.cblock = block; a.cstride = stride;
     a.causal = causal; a.scale = scale;
-    rc = launch_kv_bwd(a, D, s);
+    rc = (D == 128) ? launch_kv_bwd_tc(a, s) : launch_kv_bwd(a, D, s);
     if (rc) return rc;
     const long long N = (long long)B * Tc * Hk * D;
     rc = launch_reduce_segments(a.part, (bf16*)dck, a.nseg, N, T, Tc, Hk, D, a.seg_len, block, stride, causal, s);
@@ -317,7 +328,7 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
     if (has_swa) {
       a.dout_b = (const bf16*)dout_swa; a.lse_b = lse_swa; a.delta_b = delta_swa; a.gate_b = (const bf16*)gate_swa;
     }
-    rc = launch_kv_bwd(a, D, s);
+    rc = (D == 128 && BS == 64) ? launch_kv_bwd_tc(a, s) : launch_kv_bwd(a, D, s);
     if (rc) return rc;
   }
   return 0;

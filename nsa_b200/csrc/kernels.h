@@ -82,6 +82,9 @@ struct KvArgs {
 };
 int launch_kv_bwd(const KvArgs& a, int D, cudaStream_t s);
 int kv_status(int* out);
+// tcgen05 engine for head_dim 128 and 64-key blocks (same arguments and results)
+int launch_kv_bwd_tc(const KvArgs& a, cudaStream_t s);
+int kv_tc_status(int* out);
 
 // ---- compression ------------------------------------------------------------------------------
 struct CompressArgs {
@@ -107,6 +110,11 @@ int compress_status(int* out);
 // dW partials in the library's fixed device array instead of a caller workspace
 int launch_compress_bwd_static(const CompressArgs& a, cudaStream_t s);
 long long compress_static_scratch_floats();
+
+// tcgen05 GEMM for equal-length sequences (x [B,T,H,D], T % d == 0)
+int launch_compress_fwd_uniform(const bf16* x, const bf16* w, const bf16* bias, bf16* y, int B, int T, int H, int D, int l,
+                                int d, cudaStream_t s);
+int compress_tc_status(int* out);
 
 // ---- small helpers ----------------------------------------------------------------------------
 // delta[r] = (gate ? gate[r] : 1) * sum_d o[r,d]*dout[r,d];  dgate[r] = sum_d o[r,d]*dout[r,d]

@@ -1,0 +1,416 @@
+// Key/value-major backward on tcgen05 (head_dim 128, 64-key blocks): dK,dV of the selected + sliding-window
+// branches and dCK,dCV of the compressed branch.  Same work decomposition and reference semantics as kv_bwd.cu
+// (nsa/selection_attn.py:151-253 through a reverse index; nsa/triton_attention.py:219-318), different engine.
+//
+// One CTA owns 64 keys.  Query tokens that see them arrive in batches of 8: the 8 x 16 (token, head) rows form a
+// [128 x D] tile of Q and of dO in shared memory (8 TMA boxes of 16 rows each, 128-byte swizzle).  Per batch, one
+// thread issues four groups of tcgen05.mma (accumulators in TMEM):
+//     S   [128 rows x 64 keys] = Qg . K^T          A = Qg (K-major),  B = K  (K-major)
+//     dP  [128 rows x 64 keys] = dOg . V^T         A = dOg (K-major), B = V  (K-major)
+//     dV^T[128 d    x 64 keys] += dOg^T . (g P)    A = dOg (MN-major), B = P  (MN-major, written by the soft-max warps)
+//     dK^T[128 d    x 64 keys] += Qg^T . dS        A = Qg (MN-major),  B = dS (MN-major)
+// Four soft-max warps own one row per thread (lse, delta, gate and the causal/window mask are thread-local, no
+// shuffles): they read S and dP from TMEM, form P and dS = P (g dP - delta), and store both as bf16 tiles.
+// The MMA thread issues S/dP of batch n+1 before dV/dK of batch n, so the tensor core works while the soft-max
+// warps compute.  dV^T and dK^T stay in TMEM for the CTA's whole token stream and are stored once.
+// Every wait is bounded; on a time-out the role records an error and leaves its loop.
+#include "kernels.h"
+#include "tc.cuh"
+#include "tmap.h"
+
+namespace nsa {
+
+namespace {
+
+constexpr int D = 128;
+constexpr int kThreads = 192;              // warp 0 TMA, warp 1 MMA, warps 2-5 soft-max / epilogue
+constexpr int kTokB = 8;                   // tokens per batch (x16 heads = 128 rows)
+constexpr uint32_t KV_PANEL = 64 * 128;    // [64 keys][64 ch]
+constexpr uint32_t KV_TILE = 2 * KV_PANEL; // 16 KB
+constexpr uint32_t Q_PANEL = 128 * 128;    // [128 rows][64 ch]
+constexpr uint32_t Q_TILE = 2 * Q_PANEL;   // 32 KB
+constexpr uint32_t STAGE = 2 * Q_TILE;     // Q + dO
+constexpr uint32_t P_TILE = 128 * 128;     // [128 rows][64 keys]
+constexpr int kStages = 2;
+constexpr uint32_t kSmem = 2 * KV_TILE + kStages * STAGE + 2 * P_TILE + 256 + 1024;
+constexpr uint32_t kTmemCols = 256;        // S 0..63, dP 64..127, dV^T 128..191, dK^T 192..255
+
+struct Stream {  // the token stream of one CTA: branch A (list or range) then branch B (window range)
+  int nA, nB, ta_lo, tb_lo;
+  const int* list;
+};
+
+__device__ __forceinline__ int stream_token(const Stream& st, int br, int i) {
+  if (br == 0) {
+    if (i >= st.nA) i = st.nA - 1;
+    return st.list ? st.list[st.ta_lo + i] : st.ta_lo + i;
+  }
+  if (i >= st.nB) i = st.nB - 1;
+  return st.tb_lo + i;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+    kv_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDOa,
+                     const __grid_constant__ CUtensorMap tmDOb, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const KvArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t k_s = sbase, v_s = sbase + KV_TILE;
+  const uint32_t ring = sbase + 2 * KV_TILE;
+  const uint32_t p_s = ring + kStages * STAGE, ds_s = p_s + P_TILE;
+  const uint32_t bar_base = ds_s + P_TILE;
+  // barriers
+  const uint32_t full0 = bar_base, empty0 = bar_base + 16, kv_bar = bar_base + 32, sdp_full = bar_base + 40,
+                 sdp_free = bar_base + 48, pds_full = bar_base + 56, pds_free = bar_base + 64, acc_full = bar_base + 72,
+                 tmem_slot = bar_base + 80;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(full0 + 8 * i, 1);
+      mbar_init(empty0 + 8 * i, 1);
+    }
+    mbar_init(kv_bar, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_free, 128);
+    mbar_init(pds_full, 128);
+    mbar_init(pds_free, 1);
+    mbar_init(acc_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(sgen + (tmem_slot - sbase));
+
+  // ---- decode the work item (same mapping as kv_bwd.cu) -----------------------------------------------
+  const int G16 = (a.Hq / a.Hk) / 16;
+  int b, hk, blk, seg = 0;
+  Stream st = {0, 0, 0, 0, nullptr};
+  bool skip = false;
+  {
+    long long item = blockIdx.x;
+    const int BH = a.B * a.Hk;
+    if (MODE == 0) {
+      blk = (int)(item / BH);
+      const int bh = (int)(item % BH);
+      b = bh / a.Hk;
+      hk = bh % a.Hk;
+      const int NB = (a.T + 63) / 64;
+      if (a.rev_ptr) {
+        const int* rp = a.rev_ptr + (long long)bh * (NB + 1);
+        st.ta_lo = rp[blk];
+        st.nA = rp[blk + 1] - rp[blk];
+        st.list = a.rev_tok + (long long)bh * a.rev_cap;
+      }
+      if (a.window > 0) {
+        st.tb_lo = blk * 64;
+        st.nB = max(0, min(a.T, blk * 64 + 63 + a.window) - st.tb_lo);
+      }
+    } else {
+      seg = (int)(item % a.nseg);
+      item /= a.nseg;
+      const int NT = (a.Lk + 63) / 64;
+      blk = (int)(item % NT);
+      const int bh = (int)(item / NT);
+      b = bh / a.Hk;
+      hk = bh % a.Hk;
+      const int first = a.causal ? blk * 64 * a.cstride + a.cblock : 0;
+      st.ta_lo = max(first, seg * a.seg_len);
+      st.nA = min(a.T, (seg + 1) * a.seg_len) - st.ta_lo;
+      if (st.nA <= 0) skip = true;  // the reducer skips this segment too
+    }
+  }
+  const int key0 = blk * 64;
+  const int nbA = (st.nA + kTokB - 1) / kTokB, nbB = (st.nB + kTokB - 1) / kTokB;
+  const int nb_sub = nbA + nbB;             // batches per 16-head sub-group
+  const int nb = skip ? 0 : nb_sub * G16;   // batches of this CTA
+
+  if (!skip && warp == 0) {
+    // ------------------------------- TMA producer ------------------------------------------------
+    // Lanes 0-7 fetch the 8 token ids of a batch (one round trip, one batch ahead); lane 0 issues the copies.
+    if (lane == 0) {
+      mbar_expect_tx(kv_bar, 2 * KV_TILE);
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        tma_load_4d(k_s + p * KV_PANEL, &tmK, kv_bar, p * 64, hk, key0, b);
+        tma_load_4d(v_s + p * KV_PANEL, &tmV, kv_bar, p * 64, hk, key0, b);
+      }
+    }
+    auto batch_token = [&](int n) {
+      if (n >= nb) return 0;
+      const int m = n % nb_sub;
+      const int br = m < nbA ? 0 : 1;
+      return stream_token(st, br, (br == 0 ? m : m - nbA) * kTokB + (lane & 7));
+    };
+    int tk_next = batch_token(0);
+    for (int n = 0; n < nb; ++n) {
+      const int tk = tk_next;
+      tk_next = batch_token(n + 1);
+      const int sub = n / nb_sub, m = n % nb_sub;
+      const int br = m < nbA ? 0 : 1;
+      const int hg = hk * G16 + sub;
+      const CUtensorMap* tmDO = br == 0 ? &tmDOa : &tmDOb;
+      const int stage = n % kStages;
+      const uint32_t ph = (n / kStages) & 1;
+      const uint32_t fb = full0 + 8 * stage;
+      int good = 1;
+      if (lane == 0) {
+        good = mbar_wait(empty0 + 8 * stage, ph ^ 1, DEV_ERR_EMPTY_WAIT) ? 1 : 0;
+        if (good) mbar_expect_tx(fb, STAGE);
+      }
+      if (!__shfl_sync(0xffffffffu, good, 0)) break;
+      const uint32_t q_s = ring + stage * STAGE, do_s = q_s + Q_TILE;
+#pragma unroll
+      for (int j = 0; j < kTokB; ++j) {
+        const int t = __shfl_sync(0xffffffffu, tk, j);
+        if (lane == 0) {
+          const int qrow = (int)(((long long)b * a.T + t) * a.Hq + hg * 16);
+#pragma unroll
+          for (int p = 0; p < 2; ++p) {
+            tma_load_2d(q_s + p * Q_PANEL + j * 2048, &tmQ, fb, p * 64, qrow);
+            tma_load_2d(do_s + p * Q_PANEL + j * 2048, tmDO, fb, p * 64, qrow);
+          }
+        }
+      }
+    }
+  } else if (!skip && warp == 1) {
+    // ------------------------------- MMA issuer ----------------------------------------------------
+    if (lane == 0 && nb > 0) {
+      constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 64, 0, 0);   // both operands K-major
+      constexpr uint32_t idesc_mn = umma_idesc_bf16(128, 64, 1, 1);   // both operands MN-major
+      bool ok = mbar_wait(kv_bar, 0, DEV_ERR_FULL_WAIT);
+      auto issue_sdp = [&](int n) {
+        const uint32_t q_s = ring + (n % kStages) * STAGE, do_s = q_s + Q_TILE;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t aoff = (ks >> 2) * Q_PANEL + (ks & 3) * 32, boff = (ks >> 2) * KV_PANEL + (ks & 3) * 32;
+          umma_ss(tmem + 0, umma_smem_desc(q_s + aoff, 0, 1024), umma_smem_desc(k_s + boff, 0, 1024), idesc_kk, ks ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t aoff = (ks >> 2) * Q_PANEL + (ks & 3) * 32, boff = (ks >> 2) * KV_PANEL + (ks & 3) * 32;
+          umma_ss(tmem + 64, umma_smem_desc(do_s + aoff, 0, 1024), umma_smem_desc(v_s + boff, 0, 1024), idesc_kk, ks ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+      };
+      if (ok) ok = mbar_wait(full0, 0, DEV_ERR_FULL_WAIT);
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0);
+      }
+      for (int n = 0; ok && n < nb; ++n) {
+        if (n + 1 < nb) {
+          ok = mbar_wait(full0 + 8 * ((n + 1) % kStages), ((n + 1) / kStages) & 1, DEV_ERR_FULL_WAIT) &&
+               mbar_wait(sdp_free, n & 1, DEV_ERR_FULL_WAIT);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(n + 1);
+        }
+        ok = mbar_wait(pds_full, n & 1, DEV_ERR_FULL_WAIT);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t q_s = ring + (n % kStages) * STAGE, do_s = q_s + Q_TILE;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)   // contraction over the 128 rows, 16 per step
+          umma_ss(tmem + 128, umma_smem_desc(do_s + ks * 2048, Q_PANEL, 1024), umma_smem_desc(p_s + ks * 2048, 0, 1024),
+                  idesc_mn, (n | ks) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ss(tmem + 192, umma_smem_desc(q_s + ks * 2048, Q_PANEL, 1024), umma_smem_desc(ds_s + ks * 2048, 0, 1024),
+                  idesc_mn, (n | ks) ? 1u : 0u);
+        umma_commit(empty0 + 8 * (n % kStages));
+        umma_commit(pds_free);
+      }
+      umma_commit(acc_full);
+    }
+  } else if (!skip && warp >= 2) {
+    // ------------------------------- soft-max warps: one (token, head) row per thread --------------
+    const int quad = warp & 3;
+    const int row = 32 * quad + lane;           // TMEM lane == tile row
+    const int j = row >> 4, head = row & 15;
+    const uint32_t lane_addr = (uint32_t)(32 * quad) << 16;
+    const float sl2 = a.scale * kLog2e;
+    bool ok = true;
+    // per-row operands are fetched one batch ahead (token ids two ahead) so their latency hides behind the MMAs
+    struct RowInfo {
+      int t;
+      bool live;
+      int br;
+      float lse2, del, gv;
+    };
+    auto row_token = [&](int n, int& br, bool& live) {
+      br = 0;
+      live = false;
+      if (n >= nb) return 0;
+      const int m = n % nb_sub;
+      br = m < nbA ? 0 : 1;
+      const int i = (br == 0 ? m : m - nbA) * kTokB + j;
+      live = i < (br == 0 ? st.nA : st.nB);
+      return stream_token(st, br, i);
+    };
+    auto row_load = [&](int n, int t, int br, bool live) {
+      RowInfo r;
+      r.t = t;
+      r.live = live;
+      r.br = br;
+      r.lse2 = 0.f;
+      r.del = 0.f;
+      r.gv = 1.f;
+      if (n < nb) {
+        const int sub = n / nb_sub;
+        const long long qrow = ((long long)b * a.T + t) * a.Hq + (hk * G16 + sub) * 16 + head;
+        r.lse2 = (br == 0 ? a.lse_a : a.lse_b)[qrow] * kLog2e;
+        r.del = (br == 0 ? a.delta_a : a.delta_b)[qrow];
+        const bf16* gp = br == 0 ? a.gate_a : a.gate_b;
+        if (gp) r.gv = __bfloat162float(gp[qrow]);
+      }
+      return r;
+    };
+    int br1, br2;
+    bool live1, live2;
+    int t1 = row_token(0, br1, live1);
+    RowInfo cur = row_load(0, t1, br1, live1);
+    t1 = row_token(1, br1, live1);
+    for (int n = 0; ok && n < nb; ++n) {
+      const RowInfo ri = cur;
+      cur = row_load(n + 1, t1, br1, live1);          // operands of batch n+1
+      const int t2 = row_token(n + 2, br2, live2);    // token id of batch n+2
+      t1 = t2;
+      br1 = br2;
+      live1 = live2;
+      const int t = ri.t, br = ri.br;
+      const bool live = ri.live;
+      const float lse2 = ri.lse2, del = ri.del, gv = ri.gv;
+
+      ok = mbar_wait(sdp_full, n & 1, DEV_ERR_FULL_WAIT);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t pw[32], dw[32];   // 64 bf16 each
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float s[16], dp[16];
+        tmem_ld16(tmem + lane_addr + c * 16, s);
+        tmem_ld16(tmem + lane_addr + 64 + c * 16, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kp = key0 + c * 16 + e + u;
+            bool valid;
+            if (MODE == 0)
+              valid = (kp <= t) && (br == 0 || kp > t - a.window);
+            else
+              valid = kp < a.Lk && (!a.causal || kp * a.cstride + a.cblock <= t);
+            const float p = (live && valid && lse2 > -INFINITY) ? ex2(s[e + u] * sl2 - lse2) : 0.f;
+            pv[u] = p * gv;
+            dv[u] = p * (gv * dp[e + u] - del);
+          }
+          pw[c * 8 + e / 2] = pack_bf16(pv[0], pv[1]);
+          dw[c * 8 + e / 2] = pack_bf16(dv[0], dv[1]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(sdp_free);   // S and dP are in registers: the next batch's S/dP may overwrite TMEM
+      if (n > 0) {
+        ok = mbar_wait(pds_free, (n - 1) & 1, DEV_ERR_EMPTY_WAIT);   // dV/dK of the previous batch have read P, dS
+        if (!ok) break;
+      }
+      // row `row` of the [128 x 64] bf16 tiles: 8 chunks of 16 bytes at swizzled positions
+      uint8_t* prow = sgen + (p_s - sbase) + row * 128;
+      uint8_t* drow = sgen + (ds_s - sbase) + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int pos = (c ^ (row & 7)) * 16;
+        *reinterpret_cast<uint4*>(prow + pos) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
+        *reinterpret_cast<uint4*>(drow + pos) = make_uint4(dw[4 * c], dw[4 * c + 1], dw[4 * c + 2], dw[4 * c + 3]);
+      }
+      fence_proxy_async();
+      mbar_arrive(pds_full);
+    }
+    // ---- epilogue: dV^T / dK^T [d lanes x 64 key columns] -> global ---------------------------------------
+    if (ok && nb > 0) ok = mbar_wait(acc_full, 0, DEV_ERR_FULL_WAIT);
+    tc_fence_after();
+    const int dch = row;  // channel owned by this thread
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {   // 0: dV, 1: dK
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float vals[16];
+        if (nb > 0) {
+          tmem_ld16(tmem + lane_addr + 128 + which * 64 + c * 16, vals);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) vals[e] = 0.f;
+        }
+        const float mul = which ? a.scale : 1.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int kp = key0 + c * 16 + e;
+          if (!ok || kp >= a.Lk) continue;
+          const long long off = (((long long)b * a.Lk + kp) * a.Hk + hk) * D + dch;
+          if (MODE == 0) {
+            (which ? a.dk : a.dv)[off] = __float2bfloat16(vals[e] * mul);
+          } else {
+            const long long N = (long long)a.B * a.Lk * a.Hk * D;
+            a.part[((long long)(which ? 0 : a.nseg) + seg) * N + off] = vals[e] * mul;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <int MODE>
+int launch(const KvArgs& a, cudaStream_t s) {
+  CUtensorMap tmQ, tmA, tmB, tmK, tmV;
+  const long long qrows = (long long)a.B * a.T * a.Hq;
+  if (qrows > 0x7fffffffLL) {
+    set_error("B*T*Hq exceeds the 2^31 rows a TMA coordinate can address");
+    return -32;
+  }
+  int rc = make_tmap_rows2d(&tmQ, a.q, D, qrows, 16);
+  if (!rc) rc = make_tmap_rows2d(&tmA, a.dout_a ? a.dout_a : a.dout_b, D, qrows, 16);
+  if (!rc) rc = make_tmap_rows2d(&tmB, a.dout_b ? a.dout_b : a.dout_a, D, qrows, 16);
+  if (!rc) rc = make_tmap_rows4d(&tmK, a.k, D, a.Hk, a.Lk, a.B, 64);
+  if (!rc) rc = make_tmap_rows4d(&tmV, a.v, D, a.Hk, a.Lk, a.B, 64);
+  if (rc) return rc;
+  auto kern = kv_bwd_tc_kernel<MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+  if (e != cudaSuccess) return (int)e;
+  long long grid;
+  if (MODE == 0)
+    grid = (long long)a.B * a.Hk * ((a.T + 63) / 64);
+  else
+    grid = (long long)a.B * a.Hk * ((a.Lk + 63) / 64) * a.nseg;
+  if (grid <= 0) return 0;
+  if (grid > 0x7fffffffLL) {
+    set_error("kv backward: grid too large");
+    return -33;
+  }
+  kern<<<(unsigned)grid, kThreads, kSmem, s>>>(tmQ, tmA, tmB, tmK, tmV, a);
+  note_launches(1);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// head_dim 128 and 64-key blocks only; the caller falls back to launch_kv_bwd otherwise.
+int launch_kv_bwd_tc(const KvArgs& a, cudaStream_t s) { return a.mode == 0 ? launch<0>(a, s) : launch<1>(a, s); }
+int kv_tc_status(int* out) {
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_dev_error, sizeof(int));
+  if (e == cudaSuccess && *out) e = cudaMemcpyToSymbol(g_dev_error, &zero, sizeof(int));
+  return (int)e;
+}
+
+}  // namespace nsa

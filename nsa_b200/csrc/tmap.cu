@@ -43,6 +43,18 @@ static int encode(CUtensorMap* out, const void* base, int rank, const cuuint64_t
   return 0;
 }
 
+int make_tmap_generic(CUtensorMap* out, const void* base, int rank, const unsigned long long* dims,
+                      const unsigned long long* strides, const unsigned* box) {
+  cuuint64_t d[5], st[4];
+  cuuint32_t bx[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    bx[i] = box[i];
+    if (i) st[i - 1] = strides[i - 1];
+  }
+  return encode(out, base, rank, d, st, bx);
+}
+
 int make_tmap_rows4d(CUtensorMap* out, const void* base, int D, int H, long long N1, long long N0, int box_rows) {
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)N1, (cuuint64_t)N0};
   cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2, (cuuint64_t)N1 * H * D * 2};

@@ -14,6 +14,10 @@ int make_tmap_rows4d(CUtensorMap* out, const void* base, int D, int H, long long
 // bf16 matrix [rows][D] (D contiguous).  Box = 64 columns x `box_rows` rows, 128-byte swizzle.
 int make_tmap_rows2d(CUtensorMap* out, const void* base, int D, long long rows, int box_rows);
 
+// Generic bf16 tensor map: `rank` dims (innermost first, dim 0 contiguous), byte strides for dims 1.., box extents.
+int make_tmap_generic(CUtensorMap* out, const void* base, int rank, const unsigned long long* dims,
+                      const unsigned long long* strides, const unsigned* box);
+
 void set_error(const char* fmt, ...);
 
 // Process-wide count of kernels this library has launched (read through nsa_kernel_launch_count()).
