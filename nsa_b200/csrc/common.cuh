@@ -226,7 +226,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
     for (int i = 0; i < 256; ++i)
       if (mbar_try(bar, parity)) return true;
     if (global_timer_ns() - t0 > 2000000000ull) {
-      atomicExch(&g_dev_error, code);
+      atomicCAS(&g_dev_error, 0, code);   // keep the first failure
       return false;
     }
   }

@@ -9,8 +9,9 @@
 //     dP  [128 rows x 64 keys] = dOg . V^T         A = dOg (K-major), B = V  (K-major)
 //     dV^T[128 d    x 64 keys] += dOg^T . (g P)    A = dOg (MN-major), B = P  (MN-major, written by the soft-max warps)
 //     dK^T[128 d    x 64 keys] += Qg^T . dS        A = Qg (MN-major),  B = dS (MN-major)
-// Four soft-max warps own one row per thread (lse, delta, gate and the causal/window mask are thread-local, no
-// shuffles): they read S and dP from TMEM, form P and dS = P (g dP - delta), and store both as bf16 tiles.
+// Eight soft-max warps own half a row per thread (lse, delta, gate and the causal/window mask are thread-local, no
+// shuffles; warps 2-5 take key columns 0-31, warps 6-9 columns 32-63 of the same TMEM lanes): they read S and dP
+// from TMEM, form P and dS = P (g dP - delta), and store both as bf16 tiles.
 // The MMA thread issues S/dP of batch n+1 before dV/dK of batch n, so the tensor core works while the soft-max
 // warps compute.  dV^T and dK^T stay in TMEM for the CTA's whole token stream and are stored once.
 // Every wait is bounded; on a time-out the role records an error and leaves its loop.
@@ -23,7 +24,8 @@ namespace nsa {
 namespace {
 
 constexpr int D = 128;
-constexpr int kThreads = 192;              // warp 0 TMA, warp 1 MMA, warps 2-5 soft-max / epilogue
+constexpr int kThreads = 320;              // warp 0 TMA, warp 1 MMA, warps 2-9 soft-max / epilogue
+constexpr int kSoftThreads = 256;          // two threads per row: key columns 0-31 and 32-63
 constexpr int kTokB = 8;                   // tokens per batch (x16 heads = 128 rows)
 constexpr uint32_t KV_PANEL = 64 * 128;    // [64 keys][64 ch]
 constexpr uint32_t KV_TILE = 2 * KV_PANEL; // 16 KB
@@ -74,8 +76,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(kv_bar, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_free, 128);
-    mbar_init(pds_full, 128);
+    mbar_init(sdp_free, kSoftThreads);
+    mbar_init(pds_full, kSoftThreads);
     mbar_init(pds_free, 1);
     mbar_init(acc_full, 1);
     fence_mbar_init();
@@ -131,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (!skip && warp == 0) {
     // ------------------------------- TMA producer ------------------------------------------------
-    // Lanes 0-7 fetch the 8 token ids of a batch (one round trip, one batch ahead); lane 0 issues the copies.
+    // Lanes 0-7 fetch the 8 token ids of a batch one batch ahead; lane 0 waits for the stage and arms its barrier.
     if (lane == 0) {
       mbar_expect_tx(kv_bar, 2 * KV_TILE);
 #pragma unroll
@@ -164,16 +166,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!__shfl_sync(0xffffffffu, good, 0)) break;
       const uint32_t q_s = ring + stage * STAGE, do_s = q_s + Q_TILE;
+      // lanes 0-7 each issue the four boxes of their own token, so the issue latencies overlap
+      if (lane < kTokB) {
+        const int qrow = (int)(((long long)b * a.T + tk) * a.Hq + hg * 16);
 #pragma unroll
-      for (int j = 0; j < kTokB; ++j) {
-        const int t = __shfl_sync(0xffffffffu, tk, j);
-        if (lane == 0) {
-          const int qrow = (int)(((long long)b * a.T + t) * a.Hq + hg * 16);
-#pragma unroll
-          for (int p = 0; p < 2; ++p) {
-            tma_load_2d(q_s + p * Q_PANEL + j * 2048, &tmQ, fb, p * 64, qrow);
-            tma_load_2d(do_s + p * Q_PANEL + j * 2048, tmDO, fb, p * 64, qrow);
-          }
+        for (int p = 0; p < 2; ++p) {
+          tma_load_2d(q_s + p * Q_PANEL + lane * 2048, &tmQ, fb, p * 64, qrow);
+          tma_load_2d(do_s + p * Q_PANEL + lane * 2048, tmDO, fb, p * 64, qrow);
         }
       }
     }
@@ -230,6 +229,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (!skip && warp >= 2) {
     // ------------------------------- soft-max warps: one (token, head) row per thread --------------
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;           // which 32 key columns this thread owns
     const int row = 32 * quad + lane;           // TMEM lane == tile row
     const int j = row >> 4, head = row & 15;
     const uint32_t lane_addr = (uint32_t)(32 * quad) << 16;
@@ -289,44 +289,62 @@ __global__ void __launch_bounds__(kThreads, 1)
       ok = mbar_wait(sdp_full, n & 1, DEV_ERR_FULL_WAIT);
       if (!ok) break;
       tc_fence_after();
-      uint32_t pw[32], dw[32];   // 64 bf16 each
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float s[16], dp[16];
-        tmem_ld16(tmem + lane_addr + c * 16, s);
-        tmem_ld16(tmem + lane_addr + 64 + c * 16, dp);
+      uint32_t pw[16], dw[16];   // 32 bf16 each
+      {
+        float sv[32], dpv[32];
+        tmem_ld16(tmem + lane_addr + half * 32, *reinterpret_cast<float(*)[16]>(&sv[0]));
+        tmem_ld16(tmem + lane_addr + half * 32 + 16, *reinterpret_cast<float(*)[16]>(&sv[16]));
+        tmem_ld16(tmem + lane_addr + 64 + half * 32, *reinterpret_cast<float(*)[16]>(&dpv[0]));
+        tmem_ld16(tmem + lane_addr + 64 + half * 32 + 16, *reinterpret_cast<float(*)[16]>(&dpv[16]));
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(sdp_free);   // S and dP are in registers: the next batch's S/dP may overwrite TMEM
+        const int kfirst = key0 + half * 32, klast = kfirst + 31;
+        bool all_valid;
+        if (MODE == 0)
+          all_valid = (klast <= t) && (br == 0 || kfirst > t - a.window);
+        else
+          all_valid = klast < a.Lk && (!a.causal || klast * a.cstride + a.cblock <= t);
+        if (!live || !(lse2 > -INFINITY)) {
 #pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          float pv[2], dv[2];
+          for (int e = 0; e < 16; ++e) pw[e] = dw[e] = 0u;
+        } else if (all_valid) {
+          const float nl = -lse2;
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int kp = key0 + c * 16 + e + u;
-            bool valid;
-            if (MODE == 0)
-              valid = (kp <= t) && (br == 0 || kp > t - a.window);
-            else
-              valid = kp < a.Lk && (!a.causal || kp * a.cstride + a.cblock <= t);
-            const float p = (live && valid && lse2 > -INFINITY) ? ex2(s[e + u] * sl2 - lse2) : 0.f;
-            pv[u] = p * gv;
-            dv[u] = p * (gv * dp[e + u] - del);
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = ex2(fmaf(sv[e], sl2, nl)), p1 = ex2(fmaf(sv[e + 1], sl2, nl));
+            pw[e / 2] = pack_bf16(p0 * gv, p1 * gv);
+            dw[e / 2] = pack_bf16(p0 * fmaf(gv, dpv[e], -del), p1 * fmaf(gv, dpv[e + 1], -del));
           }
-          pw[c * 8 + e / 2] = pack_bf16(pv[0], pv[1]);
-          dw[c * 8 + e / 2] = pack_bf16(dv[0], dv[1]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float pv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int kp = kfirst + e + u;
+              bool valid;
+              if (MODE == 0)
+                valid = (kp <= t) && (br == 0 || kp > t - a.window);
+              else
+                valid = kp < a.Lk && (!a.causal || kp * a.cstride + a.cblock <= t);
+              pv[u] = valid ? ex2(sv[e + u] * sl2 - lse2) : 0.f;
+            }
+            pw[e / 2] = pack_bf16(pv[0] * gv, pv[1] * gv);
+            dw[e / 2] = pack_bf16(pv[0] * fmaf(gv, dpv[e], -del), pv[1] * fmaf(gv, dpv[e + 1], -del));
+          }
         }
       }
-      tc_fence_before();
-      mbar_arrive(sdp_free);   // S and dP are in registers: the next batch's S/dP may overwrite TMEM
       if (n > 0) {
         ok = mbar_wait(pds_free, (n - 1) & 1, DEV_ERR_EMPTY_WAIT);   // dV/dK of the previous batch have read P, dS
         if (!ok) break;
       }
-      // row `row` of the [128 x 64] bf16 tiles: 8 chunks of 16 bytes at swizzled positions
+      // this thread's half of row `row` of the [128 x 64] bf16 tiles: 4 chunks of 16 bytes at swizzled positions
       uint8_t* prow = sgen + (p_s - sbase) + row * 128;
       uint8_t* drow = sgen + (ds_s - sbase) + row * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int pos = (c ^ (row & 7)) * 16;
+      for (int c = 0; c < 4; ++c) {
+        const int pos = ((4 * half + c) ^ (row & 7)) * 16;
         *reinterpret_cast<uint4*>(prow + pos) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
         *reinterpret_cast<uint4*>(drow + pos) = make_uint4(dw[4 * c], dw[4 * c + 1], dw[4 * c + 2], dw[4 * c + 3]);
       }
@@ -337,8 +355,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (ok && nb > 0) ok = mbar_wait(acc_full, 0, DEV_ERR_FULL_WAIT);
     tc_fence_after();
     const int dch = row;  // channel owned by this thread
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {   // 0: dV, 1: dK
+    {
+      const int which = half;   // warps 2-5 store dV, warps 6-9 store dK
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float vals[16];
