@@ -64,7 +64,7 @@ int nsa_device_status(void) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(1000 + (int)e, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
   int worst = 0, v = 0;
-  int (*fns[])(int*) = {sel_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status};
+  int (*fns[])(int*) = {sel_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_tc_status};
   for (auto f : fns) {
     v = 0;
     const int rc = f(&v);
@@ -168,6 +168,7 @@ int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, flo
     a.n_pool = nsa_pool_out_len(Tc, pool_k, pool_s, pool_p);
     a.sel_idx = sel_idx; a.sel_scores = sel_scores;
   }
+  if (dense_fwd_tc_supported(a, D)) return launch_dense_fwd_tc(a, (cudaStream_t)stream);
   return launch_dense_fwd(a, D, (cudaStream_t)stream);
 }
 
@@ -246,7 +247,7 @@ int nsa_sel_swa_fwd(const void* q, const void* k, const void* v, const void* idx
     DenseArgs a = {};
     a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.o = (bf16*)o_swa; a.lse = lse_swa;
     a.B = B; a.T = T; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
-    rc = launch_dense_fwd(a, D, s);
+    rc = dense_fwd_tc_supported(a, D) ? launch_dense_fwd_tc(a, s) : launch_dense_fwd(a, D, s);
     if (rc) return rc;
   }
   if (o) {

@@ -231,6 +231,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
     }
   }
 }
+// The same with a CTA-wide abort flag in shared memory: once any wait of the CTA has given up, every later wait
+// returns false at once, so roles that must keep meeting at named barriers can run their loops to the end without
+// waiting (their results are discarded) instead of leaving a partner stuck at a barrier.
+__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, int code, volatile int* abort_flag) {
+  if (*abort_flag) return false;
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > 2000000000ull) {
+      atomicCAS(&g_dev_error, 0, code);
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1) {
   asm volatile(

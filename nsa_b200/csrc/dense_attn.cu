@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == kTok) {
     // ------------------------------- producer ------------------------------------------------
-    if (lane != 0) return;
+    // lane 0 waits for a free stage and arms its barrier; the boxes are issued one per lane
     uint32_t it = 0;
     for (long long item = blockIdx.x; item < total; item += gridDim.x) {
       const int hg = (int)(item % HG);
@@ -97,14 +97,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         const bool withv = i < sc.nAttn;
         const int jt = sc.first + (i < sc.nA ? i : i - sc.nA);
         const int stage = it % nst;
-        const uint32_t ph = (it / nst) & 1;
-        if (!mbar_wait(empty_bar(stage), ph ^ 1, DEV_ERR_EMPTY_WAIT)) return;
-        mbar_expect_tx(full_bar(stage), withv ? stage_bytes : tile_bytes);
-        const uint32_t dst = sbase + stage * stage_bytes;
-#pragma unroll
-        for (int p = 0; p < D / 64; ++p) {
-          tma_load_4d(dst + p * kPanel, &tmK, full_bar(stage), p * 64, hk, jt * 64, b);
-          if (withv) tma_load_4d(dst + tile_bytes + p * kPanel, &tmV, full_bar(stage), p * 64, hk, jt * 64, b);
+        int good = 1;
+        if (lane == 0) {
+          const uint32_t ph = (it / nst) & 1;
+          good = mbar_wait(empty_bar(stage), ph ^ 1, DEV_ERR_EMPTY_WAIT) ? 1 : 0;
+          if (good) mbar_expect_tx(full_bar(stage), withv ? stage_bytes : tile_bytes);
+        }
+        if (!__shfl_sync(0xffffffffu, good, 0)) return;
+        if (lane < 2 * (D / 64)) {
+          const uint32_t dst = sbase + stage * stage_bytes;
+          const int p = lane >> 1;
+          if (lane & 1) {
+            if (withv) tma_load_4d(dst + tile_bytes + p * kPanel, &tmV, full_bar(stage), p * 64, hk, jt * 64, b);
+          } else {
+            tma_load_4d(dst + p * kPanel, &tmK, full_bar(stage), p * 64, hk, jt * 64, b);
+          }
         }
         ++it;
       }

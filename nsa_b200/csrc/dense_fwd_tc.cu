@@ -1,0 +1,503 @@
+// Dense query-major attention FORWARD on tcgen05 (head_dim 128): sliding-window attention (mode 0) and compressed
+// attention with the fused block selection (mode 1).  Same semantics and results layout as dense_attn.cu
+// (nsa/selection_attn.py:484-516; nsa/triton_attention.py:87-181,465-475; scoring of nsa/torch_attention.py:121-125).
+//
+// A persistent CTA owns 8 consecutive tokens x the 16 heads of a GQA group = one [128 x 128] Q tile (a single 3-D
+// TMA box per 64-column panel).  [128 keys x 128] K and V tiles stream through a 2-stage mbarrier ring.  One
+// thread issues  S = Q.K^T  (M=N=K=128, accumulator in TMEM, two S buffers) and  O += P.V  (A = P from shared
+// memory, B = V as an MN-major operand).  Eight soft-max warps own half a row per thread (64 of the 128 key
+// columns of their TMEM lane): masks, running max and sum are thread-local; the two halves of a row exchange only
+// their tile maximum through shared memory.  O is rescaled in TMEM only when some row's maximum moved.
+// S of tile i+1 is issued before P.V of tile i, so the tensor core overlaps the soft-max.
+//
+// Selection (mode 1): a first pass over all compressed tiles collects the statistics of the unscaled, unmasked
+// soft-max while the causal tiles also feed the attention; a second pass recomputes S, forms p / l, pools the 5-wide
+// stride-4 windows inside the thread, sums the 16 heads with warp shuffles and accumulates a per-token score vector
+// in shared memory; eight warps then pick the top n of their token (ties to the lower block index).
+#include "kernels.h"
+#include "tc.cuh"
+#include "tmap.h"
+
+namespace nsa {
+
+namespace {
+
+constexpr int D = 128;
+constexpr int kTok = 8;
+constexpr int kThreads = 320;                 // warp 0 TMA, warp 1 MMA, warps 2-9 soft-max
+constexpr int kSoft = 256;
+constexpr uint32_t PANEL = 128 * 128;         // [128 rows][64 columns] bf16
+constexpr uint32_t TILE = 2 * PANEL;          // 32 KB
+constexpr uint32_t STAGE = 2 * TILE;          // K + V
+constexpr int kStages = 2;
+constexpr uint32_t kTmemCols = 512;           // S0 0..127, S1 128..255, O 256..383
+constexpr int kMaxPool = 512;
+
+struct Sched {
+  int first, nA, nAttn, nB;
+};
+
+template <int MODE>
+__device__ __forceinline__ Sched make_sched(const DenseArgs& a, int t0) {
+  Sched s;
+  const int tmax = min(a.T - 1, t0 + kTok - 1);
+  if (MODE == 0) {
+    s.first = max(0, t0 - a.window + 1) / 128;
+    s.nA = tmax / 128 - s.first + 1;
+    s.nAttn = s.nA;
+    s.nB = 0;
+  } else {
+    const int nt_all = (a.Lk + 127) / 128;
+    int nvis = a.Lk;
+    if (a.causal) nvis = (tmax < a.cblock) ? 0 : min(a.Lk, (tmax - a.cblock) / a.cstride + 1);
+    s.first = 0;
+    s.nAttn = (nvis + 127) / 128;
+    const bool sel = a.n_sel > 0;
+    s.nA = sel ? nt_all : s.nAttn;
+    s.nB = sel ? nt_all : 0;
+  }
+  return s;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+    dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const DenseArgs a, const int pool_floats) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t q_s = sbase, ring = sbase + TILE, p_s = ring + kStages * STAGE;
+  const uint32_t misc = p_s + TILE;
+  // misc: barriers (16 x 8 B), tmem slot, exchange buffers, pooled scores
+  const uint32_t q_full = misc, q_free = misc + 8, full0 = misc + 16, empty0 = misc + 32, s_full0 = misc + 48,
+                 s_free0 = misc + 64, p_full = misc + 80, p_free = misc + 88, o_full = misc + 96, tmem_slot = misc + 104, o_free = misc + 120;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + (misc - sbase) + 112);
+  float* xch = reinterpret_cast<float*>(sgen + (misc - sbase) + 128);  // [2 parity][2 half][128 rows]
+  float* xst = xch + 2 * 2 * 128;                                       // [2 values][2 half][128 rows]
+  float* pool = xst + 2 * 2 * 128;                                      // [kTok][pool_floats]
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    mbar_init(q_free, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(full0 + 8 * i, 1);
+      mbar_init(empty0 + 8 * i, 1);
+      mbar_init(s_full0 + 8 * i, 1);
+      mbar_init(s_free0 + 8 * i, kSoft);
+    }
+    mbar_init(p_full, kSoft);
+    mbar_init(p_free, 1);
+    mbar_init(o_full, 1);
+    mbar_init(o_free, kSoft);
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(sgen + (tmem_slot - sbase));
+
+  const int HG = a.Hq / 16;
+  const int G16 = (a.Hq / a.Hk) / 16;
+  const int ntile = (a.T + kTok - 1) / kTok;
+  const long long total = (long long)a.B * HG * ntile;
+  const bool do_sel = MODE == 1 && a.n_sel > 0;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer ------------------------------------------------
+    uint32_t c = 0, ic = 0;
+    bool alive = true;
+    for (long long item = blockIdx.x; alive && item < total; item += gridDim.x, ++ic) {
+      const int hg = (int)(item % HG);
+      const int tile = ntile - 1 - (int)((item / HG) % ntile);
+      const int b = (int)(item / ((long long)HG * ntile));
+      const int hk = hg / G16;
+      const int t0 = tile * kTok;
+      const Sched sc = make_sched<MODE>(a, t0);
+      int good = 1;
+      if (lane == 0) {
+        good = mbar_wait_abortable(q_free, (ic & 1) ^ 1, 101, abort_flag) ? 1 : 0;
+        if (good) mbar_expect_tx(q_full, TILE);
+      }
+      if (!__shfl_sync(0xffffffffu, good, 0)) break;
+      if (lane < 2) {
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(q_s + lane * PANEL), "l"(&tmQ), "r"(q_full), "r"(lane * 64), "r"(hg * 16), "r"(b * a.T + t0)
+            : "memory");
+      }
+      for (int i = 0; i < sc.nA + sc.nB; ++i, ++c) {
+        const bool withv = i < sc.nAttn;
+        const int jt = sc.first + (i < sc.nA ? i : i - sc.nA);
+        const int stage = c & 1;
+        if (lane == 0) {
+          good = mbar_wait_abortable(empty0 + 8 * stage, ((c >> 1) & 1) ^ 1, 102, abort_flag) ? 1 : 0;
+          if (good) mbar_expect_tx(full0 + 8 * stage, withv ? STAGE : TILE);
+        }
+        if (!__shfl_sync(0xffffffffu, good, 0)) {
+          alive = false;
+          break;
+        }
+        if (lane < 4) {
+          const uint32_t dst = ring + stage * STAGE;
+          const int p = lane >> 1;
+          if (lane & 1) {
+            if (withv) tma_load_4d(dst + TILE + p * PANEL, &tmV, full0 + 8 * stage, p * 64, hk, jt * 128, b);
+          } else {
+            tma_load_4d(dst + p * PANEL, &tmK, full0 + 8 * stage, p * 64, hk, jt * 128, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ----------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);
+      uint32_t c = 0, ic = 0, pc = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; ok && item < total; item += gridDim.x, ++ic) {
+        const int tile = ntile - 1 - (int)((item / (a.Hq / 16)) % ntile);
+        const Sched sc = make_sched<MODE>(a, tile * kTok);
+        const int nt = sc.nA + sc.nB;
+        ok = mbar_wait_abortable(q_full, ic & 1, 103, abort_flag);
+        auto finish = [&](uint32_t cc, int ii) {   // tile cc (item-local index ii) after its soft-max
+          const uint32_t st = cc & 1;
+          if (ii < sc.nAttn) {
+            if (!mbar_wait_abortable(p_full, pc & 1, 104, abort_flag)) return false;
+            tc_fence_after();
+            const uint32_t v_s = ring + st * STAGE + TILE;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              umma_ss(tmem + 256, umma_smem_desc(p_s + (ks >> 2) * PANEL + (ks & 3) * 32, 0, 1024),
+                      umma_smem_desc(v_s + ks * 2048, PANEL, 1024), idesc_pv, (ii | ks) ? 1u : 0u);
+            umma_commit(empty0 + 8 * st);
+            umma_commit(p_free);
+            ++pc;
+          } else {
+            umma_commit(empty0 + 8 * st);
+          }
+          return true;
+        };
+        for (int i = 0; ok && i < nt; ++i, ++c) {
+          const uint32_t st = c & 1, ph = (c >> 1) & 1;
+          ok = mbar_wait_abortable(full0 + 8 * st, ph, 105, abort_flag) && mbar_wait_abortable(s_free0 + 8 * st, ph ^ 1, 106, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t k_s = ring + st * STAGE;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
+            umma_ss(tmem + st * 128, umma_smem_desc(q_s + off, 0, 1024), umma_smem_desc(k_s + off, 0, 1024), idesc_s,
+                    ks ? 1u : 0u);
+          }
+          umma_commit(s_full0 + 8 * st);
+          if (i == nt - 1) umma_commit(q_free);
+          if (i > 0) ok = finish(c - 1, i - 1);
+        }
+        if (ok && nt > 0) ok = finish(c - 1, nt - 1);
+        if (nt == 0) umma_commit(q_free);
+        // o_full must not complete twice before the soft-max warps have seen it once: items without P.V tiles do
+        // not throttle this thread, so wait until the previous item's epilogue has been done
+        if (ok && ic > 0) ok = mbar_wait_abortable(o_free, (ic - 1) & 1, 110, abort_flag);
+        umma_commit(o_full);
+      }
+    }
+  } else {
+    // ------------------------------- soft-max warps ------------------------------------------------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;             // key columns 64*half .. +63 of each 128-key tile
+    const int row = 32 * quad + lane;             // TMEM lane == Q tile row = (token, head)
+    const int tl = row >> 4, head = row & 15;
+    const uint32_t lane_addr = (uint32_t)(32 * quad) << 16;
+    const float sl2 = a.scale * kLog2e;
+    const int sthread = threadIdx.x - 64;         // 0..255 among the soft-max threads
+    uint32_t c = 0, ic = 0, pc = 0, xp = 0;
+    bool ok = true;
+    for (long long item = blockIdx.x; item < total; item += gridDim.x, ++ic) {
+      const int hg = (int)(item % HG);
+      const int tile = ntile - 1 - (int)((item / HG) % ntile);
+      const int b = (int)(item / ((long long)HG * ntile));
+      const int t0 = tile * kTok;
+      const int t = t0 + tl;
+      const bool live = t < a.T;
+      const Sched sc = make_sched<MODE>(a, t0);
+      const int nt = sc.nA + sc.nB;
+      int nvis = a.Lk;
+      if (MODE == 1 && a.causal) nvis = (t < a.cblock) ? 0 : min(a.Lk, (t - a.cblock) / a.cstride + 1);
+      float m_run = -INFINITY, l_run = 0.f;     // attention soft-max (log2 domain), this thread's columns
+      float m2 = -INFINITY, l2 = 0.f;           // selection soft-max over raw scores, this thread's columns
+      float sel_m = 0.f, sel_inv = 0.f;         // merged statistics used by the second pass
+      if (do_sel) {
+        for (int i = sthread; i < kTok * pool_floats; i += kSoft) pool[i] = 0.f;
+      }
+      int pv_local = 0;
+      for (int i = 0; i < nt; ++i, ++c) {
+        const bool passB = i >= sc.nA;
+        const int jt = sc.first + (passB ? i - sc.nA : i);
+        const int j0 = jt * 128 + half * 64;     // first key column of this thread
+        const uint32_t st = c & 1;
+        if (do_sel && i == sc.nA) {
+          // merge the two halves' raw-score statistics before the second pass
+          xst[(0 * 2 + half) * 128 + row] = m2;
+          xst[(1 * 2 + half) * 128 + row] = l2;
+          named_bar_sync(1, kSoft);
+          const float mo = xst[(0 * 2 + (half ^ 1)) * 128 + row], lo = xst[(1 * 2 + (half ^ 1)) * 128 + row];
+          const float M = fmaxf(m2, mo);
+          const float L = (m2 > -INFINITY ? l2 * ex2((m2 - M) * kLog2e) : 0.f) + (mo > -INFINITY ? lo * ex2((mo - M) * kLog2e) : 0.f);
+          sel_m = M;
+          sel_inv = L > 0.f ? 1.f / L : 0.f;
+          named_bar_sync(1, kSoft);
+        }
+        ok = mbar_wait_abortable(s_full0 + 8 * st, (c >> 1) & 1, 107, abort_flag) && ok;
+        tc_fence_after();
+        float s[64];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          tmem_ld16(tmem + lane_addr + st * 128 + half * 64 + q4 * 16, *reinterpret_cast<float(*)[16]>(&s[q4 * 16]));
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(s_free0 + 8 * st);
+
+        if (do_sel && !passB) {
+          float mx = -INFINITY;
+#pragma unroll
+          for (int e = 0; e < 64; ++e)
+            if (j0 + e < a.Lk) mx = fmaxf(mx, s[e]);
+          const float mnew = fmaxf(m2, mx);
+          if (mnew > -INFINITY) {
+            float rs = 0.f;
+#pragma unroll
+            for (int e = 0; e < 64; ++e)
+              if (j0 + e < a.Lk) rs += ex2((s[e] - mnew) * kLog2e);
+            l2 = l2 * ex2((m2 - mnew) * kLog2e) + rs;
+            m2 = mnew;
+          }
+        }
+        if (do_sel && passB) {
+          // p = softmax(raw) of this row; pool inside the thread (block k: columns 4k..4k+4), then sum the 16 heads
+          float s4[16], f0[16];
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            float pe[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int e = 4 * k + u;
+              pe[u] = (live && j0 + e < a.Lk) ? ex2((s[e] - sel_m) * kLog2e) * sel_inv : 0.f;
+            }
+            s4[k] = (pe[0] + pe[1]) + (pe[2] + pe[3]);
+            f0[k] = pe[0];
+          }
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+#pragma unroll
+            for (int off = 1; off < 16; off <<= 1) {
+              s4[k] += __shfl_xor_sync(0xffffffffu, s4[k], off);
+              f0[k] += __shfl_xor_sync(0xffffffffu, f0[k], off);
+            }
+          }
+          if (head == 0 && live) {
+            float* pt = pool + tl * pool_floats;
+            const int b0 = j0 >> 2;   // global pooled block of k = 0
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              const int blk = b0 + k;
+              if (blk < a.n_pool) atomicAdd(pt + blk, s4[k]);               // columns 4k .. 4k+3 of block blk
+              if (blk >= 1 && blk - 1 < a.n_pool) atomicAdd(pt + blk - 1, f0[k]);  // fifth column of block blk-1
+            }
+          }
+        }
+        if (i < sc.nAttn) {
+          // ---- attention soft-max of this tile --------------------------------------------------------
+          float mx = -INFINITY;
+#pragma unroll
+          for (int e = 0; e < 64; ++e) {
+            const int j = j0 + e;
+            bool valid;
+            if (MODE == 0)
+              valid = (j <= t) && (j > t - a.window);
+            else
+              valid = j < nvis;
+            s[e] = (live && valid) ? s[e] * sl2 : -INFINITY;
+            mx = fmaxf(mx, s[e]);
+          }
+          float* xb = xch + (xp & 1) * 256;
+          xb[half * 128 + row] = mx;
+          named_bar_sync(1, kSoft);
+          mx = fmaxf(mx, xb[(half ^ 1) * 128 + row]);
+          ++xp;
+          const float mnew = fmaxf(m_run, mx);
+          const float muse = (mnew == -INFINITY) ? 0.f : mnew;
+          const float alpha = ex2(m_run - muse);   // 0 when m_run = -inf
+          float rs = 0.f;
+          uint32_t pw[32];
+#pragma unroll
+          for (int e = 0; e < 64; e += 2) {
+            const float p0 = ex2(s[e] - muse), p1 = ex2(s[e + 1] - muse);
+            rs += p0 + p1;
+            pw[e >> 1] = pack_bf16(p0, p1);
+          }
+          l_run = l_run * alpha + rs;
+          const bool moved = (mnew != m_run) && (m_run > -INFINITY);
+          m_run = mnew;
+          if (pv_local > 0) {
+            ok = mbar_wait_abortable(p_free, (pc - 1) & 1, 108, abort_flag) && ok;   // previous P.V done: P tile and O are ours
+            if (__any_sync(0xffffffffu, moved)) {
+              tc_fence_after();
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                float o[16];
+                tmem_ld16(tmem + lane_addr + 256 + half * 64 + q4 * 16, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 16; ++e) o[e] *= alpha;
+                tmem_st16(tmem + lane_addr + 256 + half * 64 + q4 * 16, o);
+              }
+              tmem_st_wait();
+              tc_fence_before();
+            }
+          }
+          uint8_t* prow = sgen + (p_s - sbase) + half * PANEL + row * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) =
+                make_uint4(pw[4 * ch], pw[4 * ch + 1], pw[4 * ch + 2], pw[4 * ch + 3]);
+          fence_proxy_async();
+          mbar_arrive(p_full);
+          ++pc;
+          ++pv_local;
+        }
+      }
+      // ---- epilogue of the item ----------------------------------------------------------------------
+      ok = mbar_wait_abortable(o_full, ic & 1, 109, abort_flag) && ok;
+      tc_fence_after();
+      {
+        float* xb = xch + (xp & 1) * 256;
+        xb[half * 128 + row] = l_run;
+        named_bar_sync(1, kSoft);
+        const float l_tot = l_run + xb[(half ^ 1) * 128 + row];
+        ++xp;
+        const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+        const long long orow = ((long long)b * a.T + t) * a.Hq + hg * 16 + head;
+        uint4 outv[8];
+        __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(outv);
+        if (pv_local > 0) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            float o[16];
+            tmem_ld16(tmem + lane_addr + 256 + half * 64 + q4 * 16, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ho[q4 * 8 + e] = __floats2bfloat162_rn(o[2 * e] * inv, o[2 * e + 1] * inv);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) outv[e] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        tc_fence_before();
+        mbar_arrive(o_free);
+        if (live && ok) {
+          uint4* dst = reinterpret_cast<uint4*>(a.o + orow * D + half * 64);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dst[e] = outv[e];
+          if (half == 0) a.lse[orow] = l_tot > 0.f ? (m_run + log2f(l_tot)) * kLn2 : -INFINITY;
+        }
+      }
+      if (do_sel) {
+        named_bar_sync(1, kSoft);   // every head's pooled contribution has landed
+        const int tw = warp - 2;    // this warp finishes token t0 + tw
+        const int tt = t0 + tw;
+        if (tt < a.T && ok) {
+          float* pt = pool + tw * pool_floats;
+          for (int blk = lane; blk < a.n_pool; blk += 32) {
+            const int lo = blk * a.pool_s - a.pool_p;
+            const int hi = min(lo + a.pool_k, a.Lk + a.pool_p);
+            const float v = pt[blk] / (float)(hi - lo);
+            pt[blk] = v;
+            if (a.sel_scores) a.sel_scores[(((long long)b * HG + hg) * a.T + tt) * a.n_pool + blk] = v;
+          }
+          __syncwarp();
+          int* out = a.sel_idx + (((long long)b * a.T + tt) * HG + hg) * a.n_sel;
+          for (int r = 0; r < a.n_sel; ++r) {
+            float bv = -2.f;
+            int bi = 0x7fffffff;
+            for (int blk = lane; blk < a.n_pool; blk += 32) {
+              const float v = pt[blk];
+              if (v > bv) {
+                bv = v;
+                bi = blk;
+              }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+              const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+              const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+              if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+              }
+            }
+            const bool found = bv > -1.5f;
+            if (lane == 0) {
+              out[r] = found ? bi : -1;
+              if (found) pt[bi] = -2.f;
+            }
+            __syncwarp();
+          }
+        }
+        named_bar_sync(1, kSoft);   // the pool is free for the next item
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <int MODE>
+int launch(const DenseArgs& a, cudaStream_t s) {
+  CUtensorMap tmQ, tmK, tmV;
+  const unsigned long long qd[3] = {(unsigned long long)D, (unsigned long long)a.Hq, (unsigned long long)a.B * a.T};
+  const unsigned long long qs[2] = {(unsigned long long)D * 2, (unsigned long long)a.Hq * D * 2};
+  const unsigned qb[3] = {64, 16, (unsigned)kTok};
+  int rc = make_tmap_generic(&tmQ, a.q, 3, qd, qs, qb);
+  if (!rc) rc = make_tmap_rows4d(&tmK, a.k, D, a.Hk, a.Lk, a.B, 128);
+  if (!rc) rc = make_tmap_rows4d(&tmV, a.v, D, a.Hk, a.Lk, a.B, 128);
+  if (rc) return rc;
+  const bool sel = MODE == 1 && a.n_sel > 0;
+  const int pool_floats = sel ? (a.n_pool + 3) / 4 * 4 : 0;
+  const int smem = (int)(TILE + kStages * STAGE + TILE) + 128 + 2 * (2 * 2 * 128 * 4) + kTok * pool_floats * 4 + 1024;
+  auto kern = dense_fwd_tc_kernel<MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return (int)e;
+  const long long total = (long long)a.B * (a.Hq / 16) * ((a.T + kTok - 1) / kTok);
+  const int grid = (int)(total < num_sms() ? total : num_sms());
+  if (grid <= 0) return 0;
+  kern<<<grid, kThreads, smem, s>>>(tmQ, tmK, tmV, a, pool_floats);
+  note_launches(1);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// True when the tcgen05 forward covers this configuration (otherwise the caller uses launch_dense_fwd).
+bool dense_fwd_tc_supported(const DenseArgs& a, int head_dim) {
+  if (head_dim != 128) return false;
+  if (a.mode == 1 && a.n_sel > 0) {
+    if (a.pool_k != 5 || a.pool_s != 4 || a.pool_p != 0) return false;
+    if (a.n_pool > kMaxPool) return false;
+  }
+  return true;
+}
+int launch_dense_fwd_tc(const DenseArgs& a, cudaStream_t s) { return a.mode == 0 ? launch<0>(a, s) : launch<1>(a, s); }
+int dense_tc_status(int* out) {
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_dev_error, sizeof(int));
+  if (e == cudaSuccess && *out) e = cudaMemcpyToSymbol(g_dev_error, &zero, sizeof(int));
+  return (int)e;
+}
+
+}  // namespace nsa

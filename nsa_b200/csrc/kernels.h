@@ -59,6 +59,10 @@ struct DenseArgs {
 int launch_dense_fwd(const DenseArgs& a, int D, cudaStream_t s);
 int launch_dense_dq(const DenseArgs& a, int D, cudaStream_t s);
 int dense_status(int* out);
+// tcgen05 forward for head_dim 128 (and, for selection, the 5/4/0 pooling of the default block sizes)
+bool dense_fwd_tc_supported(const DenseArgs& a, int head_dim);
+int launch_dense_fwd_tc(const DenseArgs& a, cudaStream_t s);
+int dense_tc_status(int* out);
 
 // ---- key/value-major backward (dK,dV of selected + sliding window; dCK,dCV of compressed) ---
 struct KvArgs {

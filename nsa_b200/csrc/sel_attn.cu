@@ -47,8 +47,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t bar_base = sbase + merge_off + (kConsumerWarps * 16 * PO + kConsumerWarps * 16 * 2) * 4;
   auto full_bar = [&](int i) { return bar_base + 8u * i; };
   auto empty_bar = [&](int i) { return bar_base + 8u * (nst + i); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + (bar_base - sbase) + 8 * 32);
 
   if (threadIdx.x == 0) {
+    *abort_flag = 0;
     for (int i = 0; i < nst; ++i) {
       mbar_init(full_bar(i), 1);
       mbar_init(empty_bar(i), kConsumerWarps);
@@ -103,21 +105,23 @@ __global__ void __launch_bounds__(kThreads, 1)
           rem &= rem - 1;
           const int blk = __shfl_sync(0xffffffffu, mine, j);
           int good = 1;
+          const int stage = it % nst;
           if (lane == 0) {
-            const int stage = it % nst;
             const uint32_t ph = (it / nst) & 1;
-            good = mbar_wait(empty_bar(stage), ph ^ 1, DEV_ERR_EMPTY_WAIT) ? 1 : 0;
-            if (good) {
-              mbar_expect_tx(full_bar(stage), stage_bytes);
-              const uint32_t dst = sbase + stage * stage_bytes;
-#pragma unroll
-              for (int p = 0; p < D / 64; ++p) {
-                tma_load_4d(dst + p * panel_bytes, &tmK, full_bar(stage), p * 64, hkv, blk * BS, b);
-                tma_load_4d(dst + tile_bytes + p * panel_bytes, &tmV, full_bar(stage), p * 64, hkv, blk * BS, b);
-              }
-            }
+            good = mbar_wait_abortable(empty_bar(stage), ph ^ 1, DEV_ERR_EMPTY_WAIT, abort_flag) ? 1 : 0;
+            if (good) mbar_expect_tx(full_bar(stage), stage_bytes);
           }
-          if (!__shfl_sync(0xffffffffu, good, 0)) return;
+          good = __shfl_sync(0xffffffffu, good, 0);
+          // one box per lane (K/V x column panel): a single thread issuing them back to back is several times slower
+          if (good && lane < 2 * (D / 64)) {
+            const uint32_t dst = sbase + stage * stage_bytes;
+            const int p = lane >> 1;
+            if (lane & 1)
+              tma_load_4d(dst + tile_bytes + p * panel_bytes, &tmV, full_bar(stage), p * 64, hkv, blk * BS, b);
+            else
+              tma_load_4d(dst + p * panel_bytes, &tmK, full_bar(stage), p * 64, hkv, blk * BS, b);
+          }
+          if (!good) return;
           ++it;
         }
       }
@@ -170,8 +174,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (blk < 0 || (long long)blk * BS > t) continue;
         const int stage = it % nst;
         const uint32_t ph = (it / nst) & 1;
-        if (!mbar_wait(full_bar(stage), ph, DEV_ERR_FULL_WAIT)) return;
-        if (active) {
+        const bool got = mbar_wait_abortable(full_bar(stage), ph, DEV_ERR_FULL_WAIT, abort_flag);
+        if (active && got) {
           const uint32_t kbase = sbase + stage * stage_bytes;
           const uint32_t vbase = kbase + tile_bytes;
           float sc[2][4];
@@ -319,7 +323,7 @@ int launch(const SelArgs& a, cudaStream_t s) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   const int stage_bytes = 2 * a.BS * D * 2;
-  const int fixed = (kConsumerWarps * 16 * (D + 8) + kConsumerWarps * 16 * 2) * 4 + 2 * 16 * 8 + 1024;
+  const int fixed = (kConsumerWarps * 16 * (D + 8) + kConsumerWarps * 16 * 2) * 4 + 2 * 16 * 8 + 64 + 1024;
   int nst = (max_smem - fixed) / stage_bytes;
   if (nst > 16) nst = 16;
   if (nst < 2) {
