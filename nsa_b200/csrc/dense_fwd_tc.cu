@@ -263,67 +263,117 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_arrive(s_free0 + 8 * st);
 
         if (do_sel && !passB) {
+          // statistics of the raw-score soft-max; only the last tile can hold columns past Lk
+          const int nval = min(64, a.Lk - j0);
           float mx = -INFINITY;
+          if (nval >= 64) {
 #pragma unroll
-          for (int e = 0; e < 64; ++e)
-            if (j0 + e < a.Lk) mx = fmaxf(mx, s[e]);
-          const float mnew = fmaxf(m2, mx);
-          if (mnew > -INFINITY) {
-            float rs = 0.f;
+            for (int e = 0; e < 64; ++e) mx = fmaxf(mx, s[e]);
+          } else {
 #pragma unroll
             for (int e = 0; e < 64; ++e)
-              if (j0 + e < a.Lk) rs += ex2((s[e] - mnew) * kLog2e);
-            l2 = l2 * ex2((m2 - mnew) * kLog2e) + rs;
+              if (e < nval) mx = fmaxf(mx, s[e]);
+          }
+          const float mnew = fmaxf(m2, mx);
+          if (mnew > -INFINITY) {
+            const float nm = -mnew * kLog2e;
+            float rs0 = 0.f, rs1 = 0.f;
+            if (nval >= 64) {
+#pragma unroll
+              for (int e = 0; e < 64; e += 2) {
+                rs0 += ex2(fmaf(s[e], kLog2e, nm));
+                rs1 += ex2(fmaf(s[e + 1], kLog2e, nm));
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 64; ++e)
+                if (e < nval) rs0 += ex2(fmaf(s[e], kLog2e, nm));
+            }
+            l2 = l2 * ex2((m2 - mnew) * kLog2e) + (rs0 + rs1);
             m2 = mnew;
           }
         }
         if (do_sel && passB) {
-          // p = softmax(raw) of this row; pool inside the thread (block k: columns 4k..4k+4), then sum the 16 heads
-          float s4[16], f0[16];
+          // p = softmax(raw) of this row; pool inside the thread (block k: columns 4k..4k+4; its fifth column is the
+          // first column of block k+1), then sum the 16 heads of the token with a halving butterfly: after four
+          // exchange steps every lane of the 16 holds two of the 32 head sums.
+          const int nval = live ? min(64, a.Lk - j0) : 0;
+          const float nm = -sel_m * kLog2e;
+          float v[32];   // v[k] = columns 4k..4k+3, v[16+k] = column 4k
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
             float pe[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               const int e = 4 * k + u;
-              pe[u] = (live && j0 + e < a.Lk) ? ex2((s[e] - sel_m) * kLog2e) * sel_inv : 0.f;
+              pe[u] = (e < nval) ? ex2(fmaf(s[e], kLog2e, nm)) * sel_inv : 0.f;
             }
-            s4[k] = (pe[0] + pe[1]) + (pe[2] + pe[3]);
-            f0[k] = pe[0];
+            v[k] = (pe[0] + pe[1]) + (pe[2] + pe[3]);
+            v[16 + k] = pe[0];
           }
+          {
+            const bool up8 = (lane & 8) != 0;
 #pragma unroll
-          for (int k = 0; k < 16; ++k) {
+            for (int x = 0; x < 16; ++x) {
+              const float send = up8 ? v[x] : v[x + 16], keep = up8 ? v[x + 16] : v[x];
+              v[x] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+            }
+            const bool up4 = (lane & 4) != 0;
 #pragma unroll
-            for (int off = 1; off < 16; off <<= 1) {
-              s4[k] += __shfl_xor_sync(0xffffffffu, s4[k], off);
-              f0[k] += __shfl_xor_sync(0xffffffffu, f0[k], off);
+            for (int x = 0; x < 8; ++x) {
+              const float send = up4 ? v[x] : v[x + 8], keep = up4 ? v[x + 8] : v[x];
+              v[x] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+            }
+            const bool up2 = (lane & 2) != 0;
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const float send = up2 ? v[x] : v[x + 4], keep = up2 ? v[x + 4] : v[x];
+              v[x] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+            }
+            const bool up1 = (lane & 1) != 0;
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+              const float send = up1 ? v[x] : v[x + 2], keep = up1 ? v[x + 2] : v[x];
+              v[x] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
             }
           }
-          if (head == 0 && live) {
+          // lane's two values are the head sums of original slots  x + 16*b8 + 8*b4 + 4*b2 + 2*b1,  x = 0, 1
+          if (live) {
+            const int slot0 = ((lane & 8) ? 16 : 0) + ((lane & 4) ? 8 : 0) + ((lane & 2) ? 4 : 0) + ((lane & 1) ? 2 : 0);
             float* pt = pool + tl * pool_floats;
             const int b0 = j0 >> 2;   // global pooled block of k = 0
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const int blk = b0 + k;
-              if (blk < a.n_pool) atomicAdd(pt + blk, s4[k]);               // columns 4k .. 4k+3 of block blk
-              if (blk >= 1 && blk - 1 < a.n_pool) atomicAdd(pt + blk - 1, f0[k]);  // fifth column of block blk-1
+            for (int x = 0; x < 2; ++x) {
+              const int slot = slot0 + x;
+              const int blk = slot < 16 ? b0 + slot : b0 + (slot - 16) - 1;   // v[16+k] feeds block k-1
+              if (blk >= 0 && blk < a.n_pool) atomicAdd(pt + blk, v[x]);
             }
           }
         }
         if (i < sc.nAttn) {
           // ---- attention soft-max of this tile --------------------------------------------------------
-          float mx = -INFINITY;
-#pragma unroll
-          for (int e = 0; e < 64; ++e) {
-            const int j = j0 + e;
-            bool valid;
-            if (MODE == 0)
-              valid = (j <= t) && (j > t - a.window);
-            else
-              valid = j < nvis;
-            s[e] = (live && valid) ? s[e] * sl2 : -INFINITY;
-            mx = fmaxf(mx, s[e]);
+          // valid columns of this thread form one interval [lo, hi) of its 64; most tiles are fully valid
+          int lo = 0, hi = 64;
+          if (MODE == 0) {
+            lo = max(0, t - a.window + 1 - j0);
+            hi = min(64, t + 1 - j0);
+          } else {
+            hi = min(64, nvis - j0);
           }
+          if (!live) hi = 0;
+          const bool full = (lo <= 0) && (hi >= 64);
+          float mx = -INFINITY;
+          if (full) {
+#pragma unroll
+            for (int e = 0; e < 64; ++e) mx = fmaxf(mx, s[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 64; ++e) {
+              if (e < lo || e >= hi) s[e] = -INFINITY;
+              mx = fmaxf(mx, s[e]);
+            }
+          }
+          mx *= sl2;   // sl2 > 0: the maximum of the scaled scores
           float* xb = xch + (xp & 1) * 256;
           xb[half * 128 + row] = mx;
           named_bar_sync(1, kSoft);
@@ -332,14 +382,16 @@ __global__ void __launch_bounds__(kThreads, 1)
           const float mnew = fmaxf(m_run, mx);
           const float muse = (mnew == -INFINITY) ? 0.f : mnew;
           const float alpha = ex2(m_run - muse);   // 0 when m_run = -inf
-          float rs = 0.f;
+          float rs0 = 0.f, rs1 = 0.f;
           uint32_t pw[32];
 #pragma unroll
           for (int e = 0; e < 64; e += 2) {
-            const float p0 = ex2(s[e] - muse), p1 = ex2(s[e + 1] - muse);
-            rs += p0 + p1;
+            const float p0 = ex2(fmaf(s[e], sl2, -muse)), p1 = ex2(fmaf(s[e + 1], sl2, -muse));
+            rs0 += p0;
+            rs1 += p1;
             pw[e >> 1] = pack_bf16(p0, p1);
           }
+          const float rs = rs0 + rs1;
           l_run = l_run * alpha + rs;
           const bool moved = (mnew != m_run) && (m_run > -INFINITY);
           m_run = mnew;
