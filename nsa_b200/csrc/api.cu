@@ -64,7 +64,7 @@ int nsa_device_status(void) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(1000 + (int)e, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
   int worst = 0, v = 0;
-  int (*fns[])(int*) = {sel_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_tc_status};
+  int (*fns[])(int*) = {sel_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_tc_status, dense_dq_tc_status};
   for (auto f : fns) {
     v = 0;
     const int rc = f(&v);
@@ -192,7 +192,7 @@ int nsa_cmp_attn_bwd(const void* q, const void* ck, const void* cv, const float*
     a.dout = (const bf16*)dout; a.delta = delta; a.gate = (const bf16*)gate; a.dq = (bf16*)dq;
     a.accumulate = accumulate_dq; a.B = B; a.T = T; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.cblock = block;
     a.cstride = stride; a.causal = causal; a.scale = scale;
-    rc = launch_dense_dq(a, D, s);
+    rc = (D == 128) ? launch_dense_dq_tc(a, s) : launch_dense_dq(a, D, s);
     if (rc) return rc;
   }
   if (dck || dcv) {
@@ -297,7 +297,7 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
       a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.lse = const_cast<float*>(lse_swa);
       a.dout = (const bf16*)dout_swa; a.delta = delta_swa; a.gate = (const bf16*)gate_swa; a.dq = (bf16*)dq;
       a.accumulate = acc; a.B = B; a.T = T; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
-      rc = launch_dense_dq(a, D, s);
+      rc = (D == 128) ? launch_dense_dq_tc(a, s) : launch_dense_dq(a, D, s);
       if (rc) return rc;
     }
   }

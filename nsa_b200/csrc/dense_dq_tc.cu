@@ -1,0 +1,351 @@
+// dQ of the dense branches on tcgen05 (head_dim 128): sliding-window attention (mode 0) and compressed attention
+// (mode 1).  Semantics of parallel_nsa_bwd_kernel_dq's window half (nsa/selection_attn.py:358-398) and of
+// _attn_bwd_only_dq (nsa/triton_attention.py:321-416); same arguments and results as launch_dense_dq.
+//
+// A persistent CTA owns 8 consecutive tokens x 16 heads = [128 x 128] tiles of Q and dO (resident for the item).
+// [128 keys x 128] K and V tiles stream through a 2-stage ring.  Per tile one thread issues
+//     S  = Q . K^T,   dP = dO . V^T        (accumulators in TMEM)
+// eight soft-max warps (half a row of 64 key columns per thread; lse, delta, gate and the mask are thread-local)
+// form  dS = P (g dP - delta)  with  P = exp(scale S - lse)  and store it as a bf16 tile, and the thread issues
+//     dQ += dS . K                          (A = dS from shared memory, B = K as an MN-major operand)
+// S/dP of tile i+1 are issued as soon as the soft-max warps hold tile i in registers, before dQ of tile i.
+#include "kernels.h"
+#include "tc.cuh"
+#include "tmap.h"
+
+namespace nsa {
+
+namespace {
+
+constexpr int D = 128;
+constexpr int kTok = 8;
+constexpr int kThreads = 320;                 // warp 0 TMA, warp 1 MMA, warps 2-9 soft-max
+constexpr int kSoft = 256;
+constexpr uint32_t PANEL = 128 * 128;         // [128 rows][64 columns] bf16
+constexpr uint32_t TILE = 2 * PANEL;          // 32 KB
+constexpr uint32_t STAGE = 2 * TILE;          // K + V
+constexpr int kStages = 2;
+constexpr uint32_t kTmemCols = 512;           // S 0..127, dP 128..255, dQ 256..383
+constexpr uint32_t kSmem = 2 * TILE + kStages * STAGE + TILE + 256 + 1024;
+
+struct Sched {
+  int first, n;
+};
+
+template <int MODE>
+__device__ __forceinline__ Sched make_sched(const DenseArgs& a, int t0) {
+  Sched s;
+  const int tmax = min(a.T - 1, t0 + kTok - 1);
+  if (MODE == 0) {
+    s.first = max(0, t0 - a.window + 1) / 128;
+    s.n = tmax / 128 - s.first + 1;
+  } else {
+    int nvis = a.Lk;
+    if (a.causal) nvis = (tmax < a.cblock) ? 0 : min(a.Lk, (tmax - a.cblock) / a.cstride + 1);
+    s.first = 0;
+    s.n = (nvis + 127) / 128;
+  }
+  return s;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+    dense_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                       const DenseArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t q_s = sbase, do_s = sbase + TILE, ring = sbase + 2 * TILE, ds_s = ring + kStages * STAGE;
+  const uint32_t misc = ds_s + TILE;
+  const uint32_t q_full = misc, q_free = misc + 8, full0 = misc + 16, empty0 = misc + 32, sdp_full = misc + 48,
+                 sdp_free = misc + 56, ds_full = misc + 64, ds_free = misc + 72, dq_full = misc + 80, dq_free = misc + 88,
+                 tmem_slot = misc + 96;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + (misc - sbase) + 104);
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    mbar_init(q_free, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(full0 + 8 * i, 1);
+      mbar_init(empty0 + 8 * i, 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_free, kSoft);
+    mbar_init(ds_full, kSoft);
+    mbar_init(ds_free, 1);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, kSoft);
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(sgen + (tmem_slot - sbase));
+
+  const int HG = a.Hq / 16;
+  const int G16 = (a.Hq / a.Hk) / 16;
+  const int ntile = (a.T + kTok - 1) / kTok;
+  const long long total = (long long)a.B * HG * ntile;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer ------------------------------------------------
+    uint32_t c = 0, ic = 0;
+    bool alive = true;
+    for (long long item = blockIdx.x; alive && item < total; item += gridDim.x, ++ic) {
+      const int hg = (int)(item % HG);
+      const int tile = ntile - 1 - (int)((item / HG) % ntile);
+      const int b = (int)(item / ((long long)HG * ntile));
+      const int hk = hg / G16;
+      const int t0 = tile * kTok;
+      const Sched sc = make_sched<MODE>(a, t0);
+      int good = 1;
+      if (lane == 0) {
+        good = mbar_wait_abortable(q_free, (ic & 1) ^ 1, 201, abort_flag) ? 1 : 0;
+        if (good) mbar_expect_tx(q_full, 2 * TILE);
+      }
+      if (!__shfl_sync(0xffffffffu, good, 0)) break;
+      if (lane < 4) {
+        const int p = lane & 1;
+        const CUtensorMap* tm = (lane & 2) ? &tmDO : &tmQ;
+        const uint32_t dst = ((lane & 2) ? do_s : q_s) + p * PANEL;
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(dst), "l"(tm), "r"(q_full), "r"(p * 64), "r"(hg * 16), "r"(b * a.T + t0)
+            : "memory");
+      }
+      for (int i = 0; i < sc.n; ++i, ++c) {
+        const int jt = sc.first + i;
+        const int stage = c & 1;
+        if (lane == 0) {
+          good = mbar_wait_abortable(empty0 + 8 * stage, ((c >> 1) & 1) ^ 1, 202, abort_flag) ? 1 : 0;
+          if (good) mbar_expect_tx(full0 + 8 * stage, STAGE);
+        }
+        if (!__shfl_sync(0xffffffffu, good, 0)) {
+          alive = false;
+          break;
+        }
+        if (lane < 4) {
+          const uint32_t dst = ring + stage * STAGE;
+          const int p = lane >> 1;
+          if (lane & 1)
+            tma_load_4d(dst + TILE + p * PANEL, &tmV, full0 + 8 * stage, p * 64, hk, jt * 128, b);
+          else
+            tma_load_4d(dst + p * PANEL, &tmK, full0 + 8 * stage, p * 64, hk, jt * 128, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ----------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, 0, 1);
+      uint32_t c = 0, ic = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; ok && item < total; item += gridDim.x, ++ic) {
+        const int tile = ntile - 1 - (int)((item / HG) % ntile);
+        const Sched sc = make_sched<MODE>(a, tile * kTok);
+        ok = mbar_wait_abortable(q_full, ic & 1, 203, abort_flag);
+        // dQ of the previous item must have been read, and dq_full must not complete twice unseen
+        if (ok && ic > 0) ok = mbar_wait_abortable(dq_free, (ic - 1) & 1, 204, abort_flag);
+        auto issue_sdp = [&](uint32_t cc) {
+          const uint32_t k_s = ring + (cc & 1) * STAGE, v_s = k_s + TILE;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
+            umma_ss(tmem + 0, umma_smem_desc(q_s + off, 0, 1024), umma_smem_desc(k_s + off, 0, 1024), idesc_s, ks ? 1u : 0u);
+          }
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
+            umma_ss(tmem + 128, umma_smem_desc(do_s + off, 0, 1024), umma_smem_desc(v_s + off, 0, 1024), idesc_s, ks ? 1u : 0u);
+          }
+          umma_commit(sdp_full);
+        };
+        if (ok && sc.n > 0) {
+          ok = mbar_wait_abortable(full0 + 8 * (c & 1), (c >> 1) & 1, 205, abort_flag);
+          if (ok && c > 0) ok = mbar_wait_abortable(sdp_free, (c - 1) & 1, 206, abort_flag);
+          if (ok) {
+            tc_fence_after();
+            issue_sdp(c);
+          }
+        }
+        for (int i = 0; ok && i < sc.n; ++i, ++c) {
+          if (i + 1 < sc.n) {
+            ok = mbar_wait_abortable(full0 + 8 * ((c + 1) & 1), ((c + 1) >> 1) & 1, 205, abort_flag) &&
+                 mbar_wait_abortable(sdp_free, c & 1, 206, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_sdp(c + 1);
+          } else {
+            umma_commit(q_free);   // every S/dP of the item has been issued: Q and dO tiles may be reloaded after them
+          }
+          ok = mbar_wait_abortable(ds_full, c & 1, 207, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t k_s = ring + (c & 1) * STAGE;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ss(tmem + 256, umma_smem_desc(ds_s + (ks >> 2) * PANEL + (ks & 3) * 32, 0, 1024),
+                    umma_smem_desc(k_s + ks * 2048, PANEL, 1024), idesc_dq, (i | ks) ? 1u : 0u);
+          umma_commit(empty0 + 8 * (c & 1));
+          umma_commit(ds_free);
+        }
+        if (sc.n == 0) umma_commit(q_free);
+        umma_commit(dq_full);
+      }
+    }
+  } else {
+    // ------------------------------- soft-max warps ------------------------------------------------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = 32 * quad + lane;
+    const int tl = row >> 4, head = row & 15;
+    const uint32_t lane_addr = (uint32_t)(32 * quad) << 16;
+    const float sl2 = a.scale * kLog2e;
+    uint32_t c = 0, ic = 0;
+    bool ok = true;
+    for (long long item = blockIdx.x; item < total; item += gridDim.x, ++ic) {
+      const int hg = (int)(item % HG);
+      const int tile = ntile - 1 - (int)((item / HG) % ntile);
+      const int b = (int)(item / ((long long)HG * ntile));
+      const int t0 = tile * kTok;
+      const int t = t0 + tl;
+      const bool live = t < a.T;
+      const Sched sc = make_sched<MODE>(a, t0);
+      int nvis = a.Lk;
+      if (MODE == 1 && a.causal) nvis = (t < a.cblock) ? 0 : min(a.Lk, (t - a.cblock) / a.cstride + 1);
+      const long long qrow = ((long long)b * a.T + (live ? t : 0)) * a.Hq + hg * 16 + head;
+      const float lse2 = a.lse[qrow] * kLog2e;
+      const float del = a.delta[qrow];
+      const float gv = a.gate ? __bfloat162float(a.gate[qrow]) : 1.f;
+      const bool dead = !live || !(lse2 > -INFINITY);
+      for (int i = 0; i < sc.n; ++i, ++c) {
+        const int j0 = (sc.first + i) * 128 + half * 64;
+        ok = mbar_wait_abortable(sdp_full, c & 1, 208, abort_flag) && ok;
+        tc_fence_after();
+        int lo = 0, hi = 64;
+        if (MODE == 0) {
+          lo = max(0, t - a.window + 1 - j0);
+          hi = min(64, t + 1 - j0);
+        } else {
+          hi = min(64, nvis - j0);
+        }
+        if (dead) hi = 0;
+        const bool full = lo <= 0 && hi >= 64;
+        uint32_t dw[32];
+        const float nl = -lse2;
+#pragma unroll
+        for (int q2 = 0; q2 < 2; ++q2) {   // two chunks of 32 columns keep the register footprint down
+          float s[32], dp[32];
+#pragma unroll
+          for (int q4 = 0; q4 < 2; ++q4) {
+            tmem_ld16(tmem + lane_addr + half * 64 + q2 * 32 + q4 * 16, *reinterpret_cast<float(*)[16]>(&s[q4 * 16]));
+            tmem_ld16(tmem + lane_addr + 128 + half * 64 + q2 * 32 + q4 * 16, *reinterpret_cast<float(*)[16]>(&dp[q4 * 16]));
+          }
+          tmem_ld_wait();
+          if (q2 == 1) {
+            tc_fence_before();
+            mbar_arrive(sdp_free);   // S and dP of this tile are in registers
+          }
+          if (full) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const float p0 = ex2(fmaf(s[e], sl2, nl)), p1 = ex2(fmaf(s[e + 1], sl2, nl));
+              dw[q2 * 16 + (e >> 1)] = pack_bf16(p0 * fmaf(gv, dp[e], -del), p1 * fmaf(gv, dp[e + 1], -del));
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const int e0 = q2 * 32 + e;
+              const float p0 = (e0 >= lo && e0 < hi) ? ex2(fmaf(s[e], sl2, nl)) : 0.f;
+              const float p1 = (e0 + 1 >= lo && e0 + 1 < hi) ? ex2(fmaf(s[e + 1], sl2, nl)) : 0.f;
+              dw[q2 * 16 + (e >> 1)] = pack_bf16(p0 * fmaf(gv, dp[e], -del), p1 * fmaf(gv, dp[e + 1], -del));
+            }
+          }
+        }
+        if (c > 0) ok = mbar_wait_abortable(ds_free, (c - 1) & 1, 209, abort_flag) && ok;   // dQ of the previous tile read dS
+        uint8_t* drow = sgen + (ds_s - sbase) + half * PANEL + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(drow + ((ch ^ (row & 7)) << 4)) =
+              make_uint4(dw[4 * ch], dw[4 * ch + 1], dw[4 * ch + 2], dw[4 * ch + 3]);
+        fence_proxy_async();
+        mbar_arrive(ds_full);
+      }
+      // ---- epilogue: dq = scale * dQ (+ previous contents) --------------------------------------------
+      ok = mbar_wait_abortable(dq_full, ic & 1, 210, abort_flag) && ok;
+      tc_fence_after();
+      uint4 outv[8];
+      __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(outv);
+      bf16* dst = a.dq + qrow * D + half * 64;
+      if (a.accumulate && live) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) outv[e] = reinterpret_cast<const uint4*>(dst)[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) outv[e] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      if (sc.n > 0) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          float o[16];
+          tmem_ld16(tmem + lane_addr + 256 + half * 64 + q4 * 16, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float2 prev = __bfloat1622float2(ho[q4 * 8 + e]);
+            ho[q4 * 8 + e] = __floats2bfloat162_rn(fmaf(o[2 * e], a.scale, prev.x), fmaf(o[2 * e + 1], a.scale, prev.y));
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_free);
+      if (live && ok) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) reinterpret_cast<uint4*>(dst)[e] = outv[e];
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <int MODE>
+int launch(const DenseArgs& a, cudaStream_t s) {
+  CUtensorMap tmQ, tmDO, tmK, tmV;
+  const unsigned long long qd[3] = {(unsigned long long)D, (unsigned long long)a.Hq, (unsigned long long)a.B * a.T};
+  const unsigned long long qs[2] = {(unsigned long long)D * 2, (unsigned long long)a.Hq * D * 2};
+  const unsigned qb[3] = {64, 16, (unsigned)kTok};
+  int rc = make_tmap_generic(&tmQ, a.q, 3, qd, qs, qb);
+  if (!rc) rc = make_tmap_generic(&tmDO, a.dout, 3, qd, qs, qb);
+  if (!rc) rc = make_tmap_rows4d(&tmK, a.k, D, a.Hk, a.Lk, a.B, 128);
+  if (!rc) rc = make_tmap_rows4d(&tmV, a.v, D, a.Hk, a.Lk, a.B, 128);
+  if (rc) return rc;
+  auto kern = dense_dq_tc_kernel<MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+  if (e != cudaSuccess) return (int)e;
+  const long long total = (long long)a.B * (a.Hq / 16) * ((a.T + kTok - 1) / kTok);
+  const int grid = (int)(total < num_sms() ? total : num_sms());
+  if (grid <= 0) return 0;
+  kern<<<grid, kThreads, kSmem, s>>>(tmQ, tmDO, tmK, tmV, a);
+  note_launches(1);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// head_dim 128 only; the caller falls back to launch_dense_dq otherwise.
+int launch_dense_dq_tc(const DenseArgs& a, cudaStream_t s) { return a.mode == 0 ? launch<0>(a, s) : launch<1>(a, s); }
+int dense_dq_tc_status(int* out) {
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_dev_error, sizeof(int));
+  if (e == cudaSuccess && *out) e = cudaMemcpyToSymbol(g_dev_error, &zero, sizeof(int));
+  return (int)e;
+}
+
+}  // namespace nsa

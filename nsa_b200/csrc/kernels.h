@@ -63,6 +63,8 @@ int dense_status(int* out);
 bool dense_fwd_tc_supported(const DenseArgs& a, int head_dim);
 int launch_dense_fwd_tc(const DenseArgs& a, cudaStream_t s);
 int dense_tc_status(int* out);
+int launch_dense_dq_tc(const DenseArgs& a, cudaStream_t s);
+int dense_dq_tc_status(int* out);
 
 // ---- key/value-major backward (dK,dV of selected + sliding window; dCK,dCV of compressed) ---
 struct KvArgs {

@@ -28,7 +28,7 @@ __device__ __forceinline__ int load_block_index(const void* idx, int idx64, long
 }
 
 template <int D, bool BWD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, BWD ? 1 : 2)
     sel_qmajor_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const SelArgs a,
                       const int nst) {
   extern __shared__ uint8_t smem_raw[];
@@ -324,7 +324,10 @@ int launch(const SelArgs& a, cudaStream_t s) {
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   const int stage_bytes = 2 * a.BS * D * 2;
   const int fixed = (kConsumerWarps * 16 * (D + 8) + kConsumerWarps * 16 * 2) * 4 + 2 * 16 * 8 + 64 + 1024;
-  int nst = (max_smem - fixed) / stage_bytes;
+  // the forward fits two CTAs per SM (168 registers): more resident warps hide the mma / ldmatrix latencies of
+  // the 16-row tiles; the dQ variant needs 244 registers and loses more to spills than it gains
+  const int per_cta = BWD ? max_smem : (max_smem - 2048) / 2;
+  int nst = (per_cta - fixed) / stage_bytes;
   if (nst > 16) nst = 16;
   if (nst < 2) {
     set_error("selected attention: not enough shared memory for two stages");
@@ -335,7 +338,8 @@ int launch(const SelArgs& a, cudaStream_t s) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
   const long long total = (long long)a.B * a.T * (a.Hq / 16);
-  const int grid = (int)(total < num_sms() ? total : num_sms());
+  const long long slots = (long long)num_sms() * (BWD ? 1 : 2);
+  const int grid = (int)(total < slots ? total : slots);
   if (grid <= 0) return 0;
   kern<<<grid, kThreads, smem, s>>>(tmK, tmV, a, nst);
   note_launches(1);
