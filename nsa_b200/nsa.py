@@ -5,39 +5,75 @@ from torch import nn
 
 from . import _lib
 from .compression_kv import KVCompressor
-from .selection_attn import ParallelNSAFunction
-from .triton_attention import _attention
 
 
-class _GatedCombine(torch.autograd.Function):
-    """o = g_slc*o_slc + g_swa*o_swa + g_cmp*o_cmp in one pass (the mul + two addcmul of
-    nsa/selection_attn.py:808-811 and nsa/nsa.py:133).  Gates [B,T,Hq], tensors [B,T,Hq,D]."""
+class _NSACore(torch.autograd.Function):
+    """Everything of NSAAttention.forward between the compression and the output, as one autograd node:
+    compressed attention + block selection, selected + sliding-window attention and the gated three-way sum
+    (nsa/nsa.py:102-133).  Keeping the three branches in one node lets the backward feed dO and the gates straight
+    to the kernels (no g*dO tensors are materialised, dQ is accumulated inside the kernels instead of by autograd)."""
 
     @staticmethod
-    def forward(ctx, o_slc, g_slc, o_swa, g_swa, o_cmp, g_cmp):
-        ts = [_lib.require(t, "combine operand") for t in (o_slc, g_slc, o_swa, g_swa, o_cmp, g_cmp)]
-        o = torch.empty_like(ts[0])
-        rows, D = o.numel() // o.shape[-1], o.shape[-1]
-        _lib.check(_lib.lib().nsa_combine(*[_lib.ptr(t) for t in ts], _lib.ptr(o), rows, D, _lib.stream()), "nsa_combine")
-        ctx.save_for_backward(*ts)
+    def forward(ctx, q, k, v, ck, cv, g_slc, g_swa, g_cmp, cfg):
+        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window) = cfg
+        q, k, v, ck, cv = (_lib.require(t, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (ck, "ck"), (cv, "cv")))
+        g_slc, g_swa, g_cmp = (_lib.require(t, "gate") for t in (g_slc, g_swa, g_cmp))
+        B, T, Hq, D = q.shape
+        Hkv, Tc = k.shape[2], ck.shape[1]
+        L, P, S = _lib.lib(), _lib.ptr, _lib.stream
+        dev = q.device
+        n_pool = L.nsa_pool_out_len(Tc, pool_k, pool_s, pool_p)
+        if n_sel > n_pool:
+            raise RuntimeError("selected index k out of range: %d blocks requested, %d exist" % (n_sel, n_pool))
+        o_cmp, o_slc, o = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+        o_swa = torch.empty_like(q) if window > 0 else None
+        lse_cmp, lse_slc = (torch.empty(B, T, Hq, dtype=torch.float32, device=dev) for _ in range(2))
+        lse_swa = torch.empty_like(lse_slc) if window > 0 else None
+        idx = torch.empty(B, T, Hkv, n_sel, dtype=torch.int32, device=dev)
+        _lib.check(L.nsa_cmp_attn_fwd(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, B, T, Tc, Hq, Hkv, D, block,
+                                      stride, 1 if causal else 0, scale, n_sel, pool_k, pool_s, pool_p, S()),
+                   "nsa_cmp_attn_fwd")
+        _lib.check(L.nsa_sel_swa_fwd(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(lse_slc), P(o_swa), P(lse_swa),
+                                     P(g_slc), P(g_swa), P(o_cmp), P(g_cmp), P(o), B, T, Hq, Hkv, D, n_sel, sel_block,
+                                     window, scale, S()), "nsa_sel_swa_fwd")
+        ctx.save_for_backward(q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx)
+        ctx.cfg = cfg
         return o
 
     @staticmethod
     def backward(ctx, do):
-        o_slc, g_slc, o_swa, g_swa, o_cmp, g_cmp = ctx.saved_tensors
+        (q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx) = ctx.saved_tensors
+        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window) = ctx.cfg
         do = _lib.require(do, "do")
-        L = _lib.lib()
-        rows, D = do.numel() // do.shape[-1], do.shape[-1]
-        grads = []
-        for o_x, g_x in ((o_slc, g_slc), (o_swa, g_swa), (o_cmp, g_cmp)):
-            d_o = torch.empty_like(do)
-            _lib.check(L.nsa_combine(_lib.ptr(do), _lib.ptr(g_x), None, None, None, None, _lib.ptr(d_o), rows, D,
-                                     _lib.stream()), "nsa_combine")
-            d_g = torch.empty_like(g_x)
-            _lib.check(L.nsa_rowdot(_lib.ptr(o_x), _lib.ptr(do), None, None, _lib.ptr(d_g), rows, D, _lib.stream()),
-                       "nsa_rowdot")
-            grads += [d_o, d_g]
-        return tuple(grads)
+        B, T, Hq, D = q.shape
+        Hkv, Tc = k.shape[2], ck.shape[1]
+        L, P, S = _lib.lib(), _lib.ptr, _lib.stream
+        dev = q.device
+        rows = B * T * Hq
+
+        def delta_and_dgate(o_x, g_x):
+            delta = torch.empty(B, T, Hq, dtype=torch.float32, device=dev)
+            dg = torch.empty_like(g_x)
+            _lib.check(L.nsa_rowdot(P(o_x), P(do), P(g_x), P(delta), P(dg), rows, D, S()), "nsa_rowdot")
+            return delta, dg
+
+        delta_slc, dg_slc = delta_and_dgate(o_slc, g_slc)
+        delta_cmp, dg_cmp = delta_and_dgate(o_cmp, g_cmp)
+        delta_swa, dg_swa = delta_and_dgate(o_swa, g_swa) if window > 0 else (None, None)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        ws_bytes = L.nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, n_sel, sel_block)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        _lib.check(L.nsa_sel_swa_bwd(P(q), P(k), P(v), P(idx), 0, None, P(do), P(lse_slc), P(delta_slc), P(g_slc),
+                                     P(do) if window > 0 else None, P(lse_swa), P(delta_swa), P(g_swa), P(dq), 0, P(dk),
+                                     P(dv), P(ws), ws_bytes, B, T, Hq, Hkv, D, n_sel, sel_block, window, scale, S()),
+                   "nsa_sel_swa_bwd")
+        dck, dcv = torch.empty_like(ck), torch.empty_like(cv)
+        ws_bytes = L.nsa_cmp_attn_bwd_workspace_bytes(B, T, Tc, Hkv, D)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        _lib.check(L.nsa_cmp_attn_bwd(P(q), P(ck), P(cv), P(lse_cmp), P(do), P(delta_cmp), P(g_cmp), P(dq), 1, P(dck),
+                                      P(dcv), P(ws), ws_bytes, B, T, Tc, Hq, Hkv, D, block, stride, 1 if causal else 0,
+                                      scale, S()), "nsa_cmp_attn_bwd")
+        return dq, dk, dv, dck, dcv, dg_slc, dg_swa, dg_cmp, None
 
 
 class NSAAttention(nn.Module):
@@ -108,18 +144,12 @@ class NSAAttention(nn.Module):
 
         # compressed keys/values stay in the compact [B,Tc,Hkv,D] form (no repeat to Hq heads)
         ck, cv, _ = self.compressor(k, v, cu_seqlens_k, None)
-        cmp_o, indices = _attention.apply(q4, ck, cv, self.compression_stride, self.compression_block, bool(causal),
-                                          scale, num_kv_head, self.pool_kernel_size, self.pool_stride,
-                                          self.pool_padding, self.selected_block_count)
-
         gating_score = self.gating(q4)                         # [B,T,Hq,3], no activation
         g_slc, g_swa, g_cmp = (g.contiguous() for g in gating_score.unbind(-1))
         k4 = k.reshape(bs, -1, num_kv_head, head_qk_dim)
         v4 = v.reshape(bs, -1, num_kv_head, head_v_dim)
-        o_slc, o_swa = ParallelNSAFunction.apply(q4, k4, v4, indices, None, self.selection_block_size,
-                                                 self.sliding_window, scale, None)
-        if o_swa is None:
-            o = o_slc * g_slc.unsqueeze(-1) + cmp_o * g_cmp.unsqueeze(-1)
-        else:
-            o = _GatedCombine.apply(o_slc, g_slc, o_swa, g_swa, cmp_o, g_cmp)
+        cfg = (self.compression_stride, self.compression_block, bool(causal), float(scale), self.pool_kernel_size,
+               self.pool_stride, self.pool_padding, self.selected_block_count, self.selection_block_size,
+               self.sliding_window)
+        o = _NSACore.apply(q4, k4, v4, ck, cv, g_slc, g_swa, g_cmp, cfg)
         return o.reshape(-1, *o.shape[-2:])
