@@ -287,14 +287,45 @@ def run_gpu(args):
             dist.all_reduce(flat)
         return o
 
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    cu1 = torch.arange(0, 2 * T, T, dtype=torch.int32, device=dev)
+
     def step_e2e():
-        qd, kd, vd, dod = (host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "do"))
-        qd.requires_grad_(True), kd.requires_grad_(True), vd.requires_grad_(True)
-        o = step(qd, kd, vd, dod)
-        out_h["o"].copy_(o.detach(), non_blocking=True)
-        out_h["dq"].copy_(qd.grad, non_blocking=True)
-        out_h["dk"].copy_(kd.grad, non_blocking=True)
-        out_h["dv"].copy_(vd.grad, non_blocking=True)
+        """The same step from pinned host buffers through the module, one sequence at a time: the host-to-device
+        copy of sequence i+1 and the device-to-host copy of sequence i-1's results overlap the compute of sequence i
+        (three streams; sequences of a batch are independent, weight gradients accumulate in .grad)."""
+        for p in params:
+            p.grad = None
+        main = torch.cuda.current_stream()
+        keep = []
+        for i in range(Bl):
+            sl = slice(i * T, (i + 1) * T)
+            with torch.cuda.stream(s_in):
+                qd, kd, vd, dod = (host[n][sl].to(dev, non_blocking=True) for n in ("q", "k", "v", "do"))
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            main.wait_event(ev_in)
+            for t_ in (qd, kd, vd, dod):
+                t_.record_stream(main)
+            qd.requires_grad_(True), kd.requires_grad_(True), vd.requires_grad_(True)
+            o = mod(qd, kd, vd, cu1, T)
+            o.backward(dod)
+            ev_c = torch.cuda.Event()
+            ev_c.record(main)
+            s_out.wait_event(ev_c)
+            for t_ in (o, qd.grad, kd.grad, vd.grad):
+                t_.record_stream(s_out)
+            with torch.cuda.stream(s_out):
+                out_h["o"][sl].copy_(o.detach(), non_blocking=True)
+                out_h["dq"][sl].copy_(qd.grad, non_blocking=True)
+                out_h["dk"][sl].copy_(kd.grad, non_blocking=True)
+                out_h["dv"][sl].copy_(vd.grad, non_blocking=True)
+            keep.append((qd, kd, vd, dod, o))
+        main.wait_stream(s_out)
+        if world > 1:
+            flat = torch.cat([p.grad.reshape(-1) for p in params])
+            dist.all_reduce(flat)
+        return keep
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):
