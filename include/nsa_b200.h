@@ -109,6 +109,33 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
                     int D, int S, int BS, int window, float scale, void* stream);
 size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS);
 
+/* ---- query shards (context parallelism) -------------------------------------------------------------
+ * No counterpart in the reference (it is single-GPU, SURVEY of its tests shows no distributed code).  The four
+ * attention entry points again, for a rank that owns only the queries q0 .. q0+Tq-1 of a T-token sequence while
+ * holding the whole K/V (and compressed K/V): every q-indexed tensor (q, o, lse, gates, indices, dout, delta, dq,
+ * sel_idx, sel_scores) has Tq rows per batch, row i being sequence position q0+i; k, v, ck, cv, dk, dv, dck, dcv
+ * keep their full lengths, and dk/dv/dck/dcv receive only this shard's contribution (sum them over ranks).
+ * Needs head_dim 128, 64-key selection blocks and the 5/4/0 pooling geometry. */
+int nsa_cmp_attn_fwd_sharded(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
+                             float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride,
+                             int causal, float scale, int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0,
+                             void* stream);
+int nsa_cmp_attn_bwd_sharded(const void* q, const void* ck, const void* cv, const float* lse, const void* dout,
+                             const float* delta, const void* gate, void* dq, int accumulate_dq, void* dck, void* dcv,
+                             void* ws, size_t ws_bytes, int B, int T, int Tc, int Hq, int Hk, int D, int block,
+                             int stride, int causal, float scale, int Tq, int q0, void* stream);
+int nsa_sel_swa_fwd_sharded(const void* q, const void* k, const void* v, const void* idx, int idx64,
+                            const int32_t* counts, void* o_slc, float* lse_slc, void* o_swa, float* lse_swa,
+                            const void* g_slc, const void* g_swa, const void* o_cmp, const void* g_cmp, void* o, int B,
+                            int T, int Hq, int Hkv, int D, int S, int BS, int window, float scale, int Tq, int q0,
+                            void* stream);
+int nsa_sel_swa_bwd_sharded(const void* q, const void* k, const void* v, const void* idx, int idx64,
+                            const int32_t* counts, const void* dout_slc, const float* lse_slc, const float* delta_slc,
+                            const void* gate_slc, const void* dout_swa, const float* lse_swa, const float* delta_swa,
+                            const void* gate_swa, void* dq, int accumulate_dq, void* dk, void* dv, void* ws,
+                            size_t ws_bytes, int B, int T, int Hq, int Hkv, int D, int S, int BS, int window,
+                            float scale, int Tq, int q0, void* stream);
+
 /* ---- helpers --------------------------------------------------------------------------------------
  * delta[r] = (gate ? gate[r] : 1) * sum_d o[r,d]*dout[r,d] (fp32, NULL to skip) and
  * dgate[r] = sum_d o[r,d]*dout[r,d] (bf16, NULL to skip); rows = B*T*Hq.

@@ -32,6 +32,11 @@ SIGNATURES = {
     "nsa_sel_swa_fwd": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),
     "nsa_sel_swa_bwd": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I, F, P]),
     "nsa_sel_swa_bwd_workspace_bytes": (Z, [I, I, I, I, I]),
+    "nsa_cmp_attn_fwd_sharded": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, I, I, P]),
+    "nsa_cmp_attn_bwd_sharded": (I, [P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I, I, F, I, I, P]),
+    "nsa_sel_swa_fwd_sharded": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P]),
+    "nsa_sel_swa_bwd_sharded": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I,
+                                    F, I, I, P]),
     "nsa_rowdot": (I, [P, P, P, P, P, L, I, P]),
     "nsa_combine": (I, [P, P, P, P, P, P, P, L, I, P]),
 }

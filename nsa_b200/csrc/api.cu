@@ -148,16 +148,19 @@ int nsa_compress_bwd_noalloc(const void* x, const void* w, const void* dy, void*
 }
 
 // ---- compressed attention ---------------------------------------------------------------------------
-int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
+static int cmp_attn_fwd_impl(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
                      float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
-                     float scale, int n_sel, int pool_k, int pool_s, int pool_p, void* stream) {
+                     float scale, int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream) {
+  const bool sharded = (Tq != T) || (q0 != 0);
+  if (Tq <= 0 || q0 < 0 || q0 + Tq > T) return fail(-12, "%s: query shard [%d, %d) is outside the sequence of %d tokens", "nsa_cmp_attn_fwd", q0, q0 + Tq, T);
+  (void)sharded;
   if (!q || !ck || !cv || !o || !lse) return fail(-1, "nsa_cmp_attn_fwd: null pointer");
   int rc = check_attn_shape("nsa_cmp_attn_fwd", B, T, Hq, Hk, D);
   if (rc) return rc;
   if (Tc <= 0) return fail(-1, "nsa_cmp_attn_fwd: no compressed positions (sequence shorter than one block)");
   DenseArgs a = {};
   a.mode = 1; a.q = (const bf16*)q; a.k = (const bf16*)ck; a.v = (const bf16*)cv; a.o = (bf16*)o; a.lse = lse;
-  a.B = B; a.T = T; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.cblock = block; a.cstride = stride; a.causal = causal;
+  a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.cblock = block; a.cstride = stride; a.causal = causal;
   a.scale = scale; a.n_sel = n_sel;
   if (n_sel > 0) {
     if (!sel_idx) return fail(-1, "nsa_cmp_attn_fwd: sel_idx is null");
@@ -169,7 +172,20 @@ int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, flo
     a.sel_idx = sel_idx; a.sel_scores = sel_scores;
   }
   if (dense_fwd_tc_supported(a, D)) return launch_dense_fwd_tc(a, (cudaStream_t)stream);
+  if (sharded) return fail(-11, "query shards need head_dim 128 and the default pooling geometry");
   return launch_dense_fwd(a, D, (cudaStream_t)stream);
+}
+
+int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
+                     float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
+                     float scale, int n_sel, int pool_k, int pool_s, int pool_p, void* stream) {
+  return cmp_attn_fwd_impl(q, ck, cv, o, lse, sel_idx, sel_scores, B, T, Tc, Hq, Hk, D, block, stride, causal, scale, n_sel, pool_k, pool_s, pool_p, T, 0, stream);
+}
+
+int nsa_cmp_attn_fwd_sharded(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
+                     float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
+                     float scale, int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream) {
+  return cmp_attn_fwd_impl(q, ck, cv, o, lse, sel_idx, sel_scores, B, T, Tc, Hq, Hk, D, block, stride, causal, scale, n_sel, pool_k, pool_s, pool_p, Tq, q0, stream);
 }
 
 size_t nsa_cmp_attn_bwd_workspace_bytes(int B, int T, int Tc, int Hk, int D) {
@@ -178,10 +194,13 @@ size_t nsa_cmp_attn_bwd_workspace_bytes(int B, int T, int Tc, int Hk, int D) {
   return (size_t)2 * nseg * B * Tc * Hk * D * sizeof(float);
 }
 
-int nsa_cmp_attn_bwd(const void* q, const void* ck, const void* cv, const float* lse, const void* dout,
+static int cmp_attn_bwd_impl(const void* q, const void* ck, const void* cv, const float* lse, const void* dout,
                      const float* delta, const void* gate, void* dq, int accumulate_dq, void* dck, void* dcv, void* ws,
                      size_t ws_bytes, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
-                     float scale, void* stream) {
+                     float scale, int Tq, int q0, void* stream) {
+  const bool sharded = (Tq != T) || (q0 != 0);
+  if (Tq <= 0 || q0 < 0 || q0 + Tq > T) return fail(-12, "%s: query shard [%d, %d) is outside the sequence of %d tokens", "nsa_cmp_attn_bwd", q0, q0 + Tq, T);
+  (void)sharded;
   if (!q || !ck || !cv || !lse || !dout || !delta) return fail(-1, "nsa_cmp_attn_bwd: null pointer");
   int rc = check_attn_shape("nsa_cmp_attn_bwd", B, T, Hq, Hk, D);
   if (rc) return rc;
@@ -190,9 +209,10 @@ int nsa_cmp_attn_bwd(const void* q, const void* ck, const void* cv, const float*
     DenseArgs a = {};
     a.mode = 1; a.q = (const bf16*)q; a.k = (const bf16*)ck; a.v = (const bf16*)cv; a.lse = const_cast<float*>(lse);
     a.dout = (const bf16*)dout; a.delta = delta; a.gate = (const bf16*)gate; a.dq = (bf16*)dq;
-    a.accumulate = accumulate_dq; a.B = B; a.T = T; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.cblock = block;
+    a.accumulate = accumulate_dq; a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.cblock = block;
     a.cstride = stride; a.causal = causal; a.scale = scale;
-    rc = (D == 128) ? launch_dense_dq_tc(a, s) : launch_dense_dq(a, D, s);
+    if (D != 128 && sharded) return fail(-11, "query shards need head_dim 128");
+      rc = (D == 128) ? launch_dense_dq_tc(a, s) : launch_dense_dq(a, D, s);
     if (rc) return rc;
   }
   if (dck || dcv) {
@@ -202,19 +222,34 @@ int nsa_cmp_attn_bwd(const void* q, const void* ck, const void* cv, const float*
     KvArgs a = {};
     a.mode = 1; a.q = (const bf16*)q; a.k = (const bf16*)ck; a.v = (const bf16*)cv;
     a.dout_a = (const bf16*)dout; a.lse_a = lse; a.delta_a = delta; a.gate_a = (const bf16*)gate;
-    a.part = (float*)ws; a.nseg = cmp_segments(T, &a.seg_len);
-    a.B = B; a.T = T; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.BS = 64; a.cblock = block; a.cstride = stride;
+    a.part = (float*)ws; a.nseg = cmp_segments(Tq, &a.seg_len);
+    a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.BS = 64; a.cblock = block; a.cstride = stride;
     a.causal = causal; a.scale = scale;
+    if (D != 128 && sharded) return fail(-11, "query shards need head_dim 128");
     rc = (D == 128) ? launch_kv_bwd_tc(a, s) : launch_kv_bwd(a, D, s);
     if (rc) return rc;
     const long long N = (long long)B * Tc * Hk * D;
-    rc = launch_reduce_segments(a.part, (bf16*)dck, a.nseg, N, T, Tc, Hk, D, a.seg_len, block, stride, causal, s);
+    rc = launch_reduce_segments(a.part, (bf16*)dck, a.nseg, N, q0, Tq, Tc, Hk, D, a.seg_len, block, stride, causal, s);
     if (rc) return rc;
-    rc = launch_reduce_segments(a.part + (long long)a.nseg * N, (bf16*)dcv, a.nseg, N, T, Tc, Hk, D, a.seg_len, block,
+    rc = launch_reduce_segments(a.part + (long long)a.nseg * N, (bf16*)dcv, a.nseg, N, q0, Tq, Tc, Hk, D, a.seg_len, block,
                                 stride, causal, s);
     if (rc) return rc;
   }
   return 0;
+}
+
+int nsa_cmp_attn_bwd(const void* q, const void* ck, const void* cv, const float* lse, const void* dout,
+                     const float* delta, const void* gate, void* dq, int accumulate_dq, void* dck, void* dcv, void* ws,
+                     size_t ws_bytes, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
+                     float scale, void* stream) {
+  return cmp_attn_bwd_impl(q, ck, cv, lse, dout, delta, gate, dq, accumulate_dq, dck, dcv, ws, ws_bytes, B, T, Tc, Hq, Hk, D, block, stride, causal, scale, T, 0, stream);
+}
+
+int nsa_cmp_attn_bwd_sharded(const void* q, const void* ck, const void* cv, const float* lse, const void* dout,
+                     const float* delta, const void* gate, void* dq, int accumulate_dq, void* dck, void* dcv, void* ws,
+                     size_t ws_bytes, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
+                     float scale, int Tq, int q0, void* stream) {
+  return cmp_attn_bwd_impl(q, ck, cv, lse, dout, delta, gate, dq, accumulate_dq, dck, dcv, ws, ws_bytes, B, T, Tc, Hq, Hk, D, block, stride, causal, scale, Tq, q0, stream);
 }
 
 // ---- selected + sliding window ----------------------------------------------------------------------
@@ -223,10 +258,13 @@ static int check_bs(const char* who, int BS) {
   return 0;
 }
 
-int nsa_sel_swa_fwd(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+static int sel_swa_fwd_impl(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
                     void* o_slc, float* lse_slc, void* o_swa, float* lse_swa, const void* g_slc, const void* g_swa,
                     const void* o_cmp, const void* g_cmp, void* o, int B, int T, int Hq, int Hkv, int D, int S, int BS,
-                    int window, float scale, void* stream) {
+                    int window, float scale, int Tq, int q0, void* stream) {
+  const bool sharded = (Tq != T) || (q0 != 0);
+  if (Tq <= 0 || q0 < 0 || q0 + Tq > T) return fail(-12, "%s: query shard [%d, %d) is outside the sequence of %d tokens", "nsa_sel_swa_fwd", q0, q0 + Tq, T);
+  (void)sharded;
   if (!q || !k || !v) return fail(-1, "nsa_sel_swa_fwd: null pointer");
   int rc = check_attn_shape("nsa_sel_swa_fwd", B, T, Hq, Hkv, D);
   if (rc) return rc;
@@ -238,7 +276,7 @@ int nsa_sel_swa_fwd(const void* q, const void* k, const void* v, const void* idx
     if (S <= 0) return fail(-1, "nsa_sel_swa_fwd: no selected blocks");
     SelArgs a = {};
     a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64; a.counts = counts;
-    a.o = (bf16*)o_slc; a.lse = lse_slc; a.B = B; a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS; a.scale = scale;
+    a.o = (bf16*)o_slc; a.lse = lse_slc; a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS; a.scale = scale;
     rc = launch_sel_fwd(a, D, s);
     if (rc) return rc;
   }
@@ -246,16 +284,31 @@ int nsa_sel_swa_fwd(const void* q, const void* k, const void* v, const void* idx
     if (!o_swa || !lse_swa) return fail(-1, "nsa_sel_swa_fwd: o_swa / lse_swa is null");
     DenseArgs a = {};
     a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.o = (bf16*)o_swa; a.lse = lse_swa;
-    a.B = B; a.T = T; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
+    a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
+    if (!dense_fwd_tc_supported(a, D) && sharded) return fail(-11, "query shards need head_dim 128");
     rc = dense_fwd_tc_supported(a, D) ? launch_dense_fwd_tc(a, s) : launch_dense_fwd(a, D, s);
     if (rc) return rc;
   }
   if (o) {
     rc = launch_combine((const bf16*)o_slc, (const bf16*)g_slc, window > 0 ? (const bf16*)o_swa : nullptr,
-                        (const bf16*)g_swa, (const bf16*)o_cmp, (const bf16*)g_cmp, (bf16*)o, (long long)B * T * Hq, D, s);
+                        (const bf16*)g_swa, (const bf16*)o_cmp, (const bf16*)g_cmp, (bf16*)o, (long long)B * Tq * Hq, D, s);
     if (rc) return rc;
   }
   return 0;
+}
+
+int nsa_sel_swa_fwd(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                    void* o_slc, float* lse_slc, void* o_swa, float* lse_swa, const void* g_slc, const void* g_swa,
+                    const void* o_cmp, const void* g_cmp, void* o, int B, int T, int Hq, int Hkv, int D, int S, int BS,
+                    int window, float scale, void* stream) {
+  return sel_swa_fwd_impl(q, k, v, idx, idx64, counts, o_slc, lse_slc, o_swa, lse_swa, g_slc, g_swa, o_cmp, g_cmp, o, B, T, Hq, Hkv, D, S, BS, window, scale, T, 0, stream);
+}
+
+int nsa_sel_swa_fwd_sharded(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                    void* o_slc, float* lse_slc, void* o_swa, float* lse_swa, const void* g_slc, const void* g_swa,
+                    const void* o_cmp, const void* g_cmp, void* o, int B, int T, int Hq, int Hkv, int D, int S, int BS,
+                    int window, float scale, int Tq, int q0, void* stream) {
+  return sel_swa_fwd_impl(q, k, v, idx, idx64, counts, o_slc, lse_slc, o_swa, lse_swa, g_slc, g_swa, o_cmp, g_cmp, o, B, T, Hq, Hkv, D, S, BS, window, scale, Tq, q0, stream);
 }
 
 size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS) {
@@ -265,11 +318,14 @@ size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS) {
   return align_up(bh * NB * NB * 4, 256) + align_up(bh * (NB + 1) * 4, 256) + align_up(bh * (size_t)T * S * 4, 256);
 }
 
-int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
                     const void* dout_slc, const float* lse_slc, const float* delta_slc, const void* gate_slc,
                     const void* dout_swa, const float* lse_swa, const float* delta_swa, const void* gate_swa, void* dq,
                     int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
-                    int D, int S, int BS, int window, float scale, void* stream) {
+                    int D, int S, int BS, int window, float scale, int Tq, int q0, void* stream) {
+  const bool sharded = (Tq != T) || (q0 != 0);
+  if (Tq <= 0 || q0 < 0 || q0 + Tq > T) return fail(-12, "%s: query shard [%d, %d) is outside the sequence of %d tokens", "nsa_sel_swa_bwd", q0, q0 + Tq, T);
+  (void)sharded;
   if (!q || !k || !v) return fail(-1, "nsa_sel_swa_bwd: null pointer");
   int rc = check_attn_shape("nsa_sel_swa_bwd", B, T, Hq, Hkv, D);
   if (rc) return rc;
@@ -287,7 +343,7 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
       a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64; a.counts = counts;
       a.lse = const_cast<float*>(lse_slc); a.dout = (const bf16*)dout_slc; a.delta = delta_slc;
       a.gate = (const bf16*)gate_slc; a.dq = (bf16*)dq; a.accumulate = acc;
-      a.B = B; a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS; a.scale = scale;
+      a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS; a.scale = scale;
       rc = launch_sel_dq(a, D, s);
       if (rc) return rc;
       acc = 1;
@@ -296,7 +352,8 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
       DenseArgs a = {};
       a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.lse = const_cast<float*>(lse_swa);
       a.dout = (const bf16*)dout_swa; a.delta = delta_swa; a.gate = (const bf16*)gate_swa; a.dq = (bf16*)dq;
-      a.accumulate = acc; a.B = B; a.T = T; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
+      a.accumulate = acc; a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
+      if (D != 128 && sharded) return fail(-11, "query shards need head_dim 128");
       rc = (D == 128) ? launch_dense_dq_tc(a, s) : launch_dense_dq(a, D, s);
       if (rc) return rc;
     }
@@ -305,7 +362,7 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
     if (!dk || !dv) return fail(-1, "nsa_sel_swa_bwd: dk and dv must be given together");
     KvArgs a = {};
     a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v;
-    a.B = B; a.T = T; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.BS = BS; a.window = has_swa ? window : 0; a.scale = scale;
+    a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.BS = BS; a.window = has_swa ? window : 0; a.scale = scale;
     a.dk = (bf16*)dk; a.dv = (bf16*)dv;
     if (has_slc) {
       if (!ws || ws_bytes < nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, S, BS))
@@ -314,13 +371,13 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
       const size_t bh = (size_t)B * Hkv;
       char* p = (char*)ws;
       RevArgs r = {};
-      r.idx = idx; r.idx64 = idx64; r.counts = counts; r.B = B; r.T = T; r.H = Hkv; r.S = S; r.BS = BS; r.NB = NB;
+      r.idx = idx; r.idx64 = idx64; r.counts = counts; r.B = B; r.T = T; r.Tq = Tq; r.q0 = q0; r.H = Hkv; r.S = S; r.BS = BS; r.NB = NB;
       r.hist = (int*)p;
       p += align_up(bh * NB * NB * 4, 256);
       r.rev_ptr = (int*)p;
       p += align_up(bh * (NB + 1) * 4, 256);
       r.rev_tok = (int*)p;
-      r.cap = (long long)T * S;
+      r.cap = (long long)Tq * S;
       rc = launch_build_rev(r, s);
       if (rc) return rc;
       a.rev_ptr = r.rev_ptr; a.rev_tok = r.rev_tok; a.rev_cap = r.cap;
@@ -329,10 +386,27 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
     if (has_swa) {
       a.dout_b = (const bf16*)dout_swa; a.lse_b = lse_swa; a.delta_b = delta_swa; a.gate_b = (const bf16*)gate_swa;
     }
+    if (!(D == 128 && BS == 64) && sharded) return fail(-11, "query shards need head_dim 128 and 64-key selection blocks");
     rc = (D == 128 && BS == 64) ? launch_kv_bwd_tc(a, s) : launch_kv_bwd(a, D, s);
     if (rc) return rc;
   }
   return 0;
+}
+
+int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                    const void* dout_slc, const float* lse_slc, const float* delta_slc, const void* gate_slc,
+                    const void* dout_swa, const float* lse_swa, const float* delta_swa, const void* gate_swa, void* dq,
+                    int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
+                    int D, int S, int BS, int window, float scale, void* stream) {
+  return sel_swa_bwd_impl(q, k, v, idx, idx64, counts, dout_slc, lse_slc, delta_slc, gate_slc, dout_swa, lse_swa, delta_swa, gate_swa, dq, accumulate_dq, dk, dv, ws, ws_bytes, B, T, Hq, Hkv, D, S, BS, window, scale, T, 0, stream);
+}
+
+int nsa_sel_swa_bwd_sharded(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                    const void* dout_slc, const float* lse_slc, const float* delta_slc, const void* gate_slc,
+                    const void* dout_swa, const float* lse_swa, const float* delta_swa, const void* gate_swa, void* dq,
+                    int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
+                    int D, int S, int BS, int window, float scale, int Tq, int q0, void* stream) {
+  return sel_swa_bwd_impl(q, k, v, idx, idx64, counts, dout_slc, lse_slc, delta_slc, gate_slc, dout_swa, lse_swa, delta_swa, gate_swa, dq, accumulate_dq, dk, dv, ws, ws_bytes, B, T, Hq, Hkv, D, S, BS, window, scale, Tq, q0, stream);
 }
 
 // ---- helpers ------------------------------------------------------------------------------------------

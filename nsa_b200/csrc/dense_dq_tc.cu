@@ -35,7 +35,7 @@ struct Sched {
 template <int MODE>
 __device__ __forceinline__ Sched make_sched(const DenseArgs& a, int t0) {
   Sched s;
-  const int tmax = min(a.T - 1, t0 + kTok - 1);
+  const int tmax = min(a.q0 + a.Tq - 1, t0 + kTok - 1);   // t0 is a sequence position
   if (MODE == 0) {
     s.first = max(0, t0 - a.window + 1) / 128;
     s.n = tmax / 128 - s.first + 1;
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int HG = a.Hq / 16;
   const int G16 = (a.Hq / a.Hk) / 16;
-  const int ntile = (a.T + kTok - 1) / kTok;
+  const int ntile = (a.Tq + kTok - 1) / kTok;
   const long long total = (long long)a.B * HG * ntile;
 
   if (warp == 0) {
@@ -100,8 +100,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int tile = ntile - 1 - (int)((item / HG) % ntile);
       const int b = (int)(item / ((long long)HG * ntile));
       const int hk = hg / G16;
-      const int t0 = tile * kTok;
-      const Sched sc = make_sched<MODE>(a, t0);
+      const int t0l = tile * kTok;             // first local query row of the item
+      const Sched sc = make_sched<MODE>(a, a.q0 + t0l);
       int good = 1;
       if (lane == 0) {
         good = mbar_wait_abortable(q_free, (ic & 1) ^ 1, 201, abort_flag) ? 1 : 0;
@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t dst = ((lane & 2) ? do_s : q_s) + p * PANEL;
         asm volatile(
             "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-            ::"r"(dst), "l"(tm), "r"(q_full), "r"(p * 64), "r"(hg * 16), "r"(b * a.T + t0)
+            ::"r"(dst), "l"(tm), "r"(q_full), "r"(p * 64), "r"(hg * 16), "r"(b * a.Tq + t0l)
             : "memory");
       }
       for (int i = 0; i < sc.n; ++i, ++c) {
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (long long item = blockIdx.x; ok && item < total; item += gridDim.x, ++ic) {
         const int tile = ntile - 1 - (int)((item / HG) % ntile);
-        const Sched sc = make_sched<MODE>(a, tile * kTok);
+        const Sched sc = make_sched<MODE>(a, a.q0 + tile * kTok);
         ok = mbar_wait_abortable(q_full, ic & 1, 203, abort_flag);
         // dQ of the previous item must have been read, and dq_full must not complete twice unseen
         if (ok && ic > 0) ok = mbar_wait_abortable(dq_free, (ic - 1) & 1, 204, abort_flag);
@@ -212,13 +212,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int hg = (int)(item % HG);
       const int tile = ntile - 1 - (int)((item / HG) % ntile);
       const int b = (int)(item / ((long long)HG * ntile));
-      const int t0 = tile * kTok;
-      const int t = t0 + tl;
-      const bool live = t < a.T;
-      const Sched sc = make_sched<MODE>(a, t0);
+      const int t0l = tile * kTok;
+      const int tloc = t0l + tl;               // local query row
+      const int t = a.q0 + tloc;               // its sequence position
+      const bool live = tloc < a.Tq;
+      const Sched sc = make_sched<MODE>(a, a.q0 + t0l);
       int nvis = a.Lk;
       if (MODE == 1 && a.causal) nvis = (t < a.cblock) ? 0 : min(a.Lk, (t - a.cblock) / a.cstride + 1);
-      const long long qrow = ((long long)b * a.T + (live ? t : 0)) * a.Hq + hg * 16 + head;
+      const long long qrow = ((long long)b * a.Tq + (live ? tloc : 0)) * a.Hq + hg * 16 + head;
       const float lse2 = a.lse[qrow] * kLog2e;
       const float del = a.delta[qrow];
       const float gv = a.gate ? __bfloat162float(a.gate[qrow]) : 1.f;
@@ -318,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 template <int MODE>
 int launch(const DenseArgs& a, cudaStream_t s) {
   CUtensorMap tmQ, tmDO, tmK, tmV;
-  const unsigned long long qd[3] = {(unsigned long long)D, (unsigned long long)a.Hq, (unsigned long long)a.B * a.T};
+  const unsigned long long qd[3] = {(unsigned long long)D, (unsigned long long)a.Hq, (unsigned long long)a.B * a.Tq};
   const unsigned long long qs[2] = {(unsigned long long)D * 2, (unsigned long long)a.Hq * D * 2};
   const unsigned qb[3] = {64, 16, (unsigned)kTok};
   int rc = make_tmap_generic(&tmQ, a.q, 3, qd, qs, qb);
@@ -329,7 +330,7 @@ int launch(const DenseArgs& a, cudaStream_t s) {
   auto kern = dense_dq_tc_kernel<MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
   if (e != cudaSuccess) return (int)e;
-  const long long total = (long long)a.B * (a.Hq / 16) * ((a.T + kTok - 1) / kTok);
+  const long long total = (long long)a.B * (a.Hq / 16) * ((a.Tq + kTok - 1) / kTok);
   const int grid = (int)(total < num_sms() ? total : num_sms());
   if (grid <= 0) return 0;
   kern<<<grid, kThreads, kSmem, s>>>(tmQ, tmDO, tmK, tmV, a);

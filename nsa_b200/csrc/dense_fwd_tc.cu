@@ -40,7 +40,7 @@ struct Sched {
 template <int MODE>
 __device__ __forceinline__ Sched make_sched(const DenseArgs& a, int t0) {
   Sched s;
-  const int tmax = min(a.T - 1, t0 + kTok - 1);
+  const int tmax = min(a.q0 + a.Tq - 1, t0 + kTok - 1);   // t0 is a sequence position
   if (MODE == 0) {
     s.first = max(0, t0 - a.window + 1) / 128;
     s.nA = tmax / 128 - s.first + 1;
@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int HG = a.Hq / 16;
   const int G16 = (a.Hq / a.Hk) / 16;
-  const int ntile = (a.T + kTok - 1) / kTok;
+  const int ntile = (a.Tq + kTok - 1) / kTok;
   const long long total = (long long)a.B * HG * ntile;
   const bool do_sel = MODE == 1 && a.n_sel > 0;
 
@@ -115,8 +115,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int tile = ntile - 1 - (int)((item / HG) % ntile);
       const int b = (int)(item / ((long long)HG * ntile));
       const int hk = hg / G16;
-      const int t0 = tile * kTok;
-      const Sched sc = make_sched<MODE>(a, t0);
+      const int t0l = tile * kTok;             // first local query row of the item
+      const Sched sc = make_sched<MODE>(a, a.q0 + t0l);
       int good = 1;
       if (lane == 0) {
         good = mbar_wait_abortable(q_free, (ic & 1) ^ 1, 101, abort_flag) ? 1 : 0;
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (lane < 2) {
         asm volatile(
             "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-            ::"r"(q_s + lane * PANEL), "l"(&tmQ), "r"(q_full), "r"(lane * 64), "r"(hg * 16), "r"(b * a.T + t0)
+            ::"r"(q_s + lane * PANEL), "l"(&tmQ), "r"(q_full), "r"(lane * 64), "r"(hg * 16), "r"(b * a.Tq + t0l)
             : "memory");
       }
       for (int i = 0; i < sc.nA + sc.nB; ++i, ++c) {
@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (long long item = blockIdx.x; ok && item < total; item += gridDim.x, ++ic) {
         const int tile = ntile - 1 - (int)((item / (a.Hq / 16)) % ntile);
-        const Sched sc = make_sched<MODE>(a, tile * kTok);
+        const Sched sc = make_sched<MODE>(a, a.q0 + tile * kTok);
         const int nt = sc.nA + sc.nB;
         ok = mbar_wait_abortable(q_full, ic & 1, 103, abort_flag);
         auto finish = [&](uint32_t cc, int ii) {   // tile cc (item-local index ii) after its soft-max
@@ -221,10 +221,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int hg = (int)(item % HG);
       const int tile = ntile - 1 - (int)((item / HG) % ntile);
       const int b = (int)(item / ((long long)HG * ntile));
-      const int t0 = tile * kTok;
-      const int t = t0 + tl;
-      const bool live = t < a.T;
-      const Sched sc = make_sched<MODE>(a, t0);
+      const int t0l = tile * kTok;
+      const int tloc = t0l + tl;               // local query row
+      const int t = a.q0 + tloc;               // its sequence position
+      const bool live = tloc < a.Tq;
+      const Sched sc = make_sched<MODE>(a, a.q0 + t0l);
       const int nt = sc.nA + sc.nB;
       int nvis = a.Lk;
       if (MODE == 1 && a.causal) nvis = (t < a.cblock) ? 0 : min(a.Lk, (t - a.cblock) / a.cstride + 1);
@@ -433,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const float l_tot = l_run + xb[(half ^ 1) * 128 + row];
         ++xp;
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-        const long long orow = ((long long)b * a.T + t) * a.Hq + hg * 16 + head;
+        const long long orow = ((long long)b * a.Tq + tloc) * a.Hq + hg * 16 + head;
         uint4 outv[8];
         __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(outv);
         if (pv_local > 0) {
@@ -461,18 +462,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (do_sel) {
         named_bar_sync(1, kSoft);   // every head's pooled contribution has landed
         const int tw = warp - 2;    // this warp finishes token t0 + tw
-        const int tt = t0 + tw;
-        if (tt < a.T && ok) {
+        const int tt = t0l + tw;   // local row of the token this warp finishes
+        if (tt < a.Tq && ok) {
           float* pt = pool + tw * pool_floats;
           for (int blk = lane; blk < a.n_pool; blk += 32) {
             const int lo = blk * a.pool_s - a.pool_p;
             const int hi = min(lo + a.pool_k, a.Lk + a.pool_p);
             const float v = pt[blk] / (float)(hi - lo);
             pt[blk] = v;
-            if (a.sel_scores) a.sel_scores[(((long long)b * HG + hg) * a.T + tt) * a.n_pool + blk] = v;
+            if (a.sel_scores) a.sel_scores[(((long long)b * HG + hg) * a.Tq + tt) * a.n_pool + blk] = v;
           }
           __syncwarp();
-          int* out = a.sel_idx + (((long long)b * a.T + tt) * HG + hg) * a.n_sel;
+          int* out = a.sel_idx + (((long long)b * a.Tq + tt) * HG + hg) * a.n_sel;
           for (int r = 0; r < a.n_sel; ++r) {
             float bv = -2.f;
             int bi = 0x7fffffff;
@@ -512,7 +513,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 template <int MODE>
 int launch(const DenseArgs& a, cudaStream_t s) {
   CUtensorMap tmQ, tmK, tmV;
-  const unsigned long long qd[3] = {(unsigned long long)D, (unsigned long long)a.Hq, (unsigned long long)a.B * a.T};
+  const unsigned long long qd[3] = {(unsigned long long)D, (unsigned long long)a.Hq, (unsigned long long)a.B * a.Tq};
   const unsigned long long qs[2] = {(unsigned long long)D * 2, (unsigned long long)a.Hq * D * 2};
   const unsigned qb[3] = {64, 16, (unsigned)kTok};
   int rc = make_tmap_generic(&tmQ, a.q, 3, qd, qs, qb);
@@ -525,7 +526,7 @@ int launch(const DenseArgs& a, cudaStream_t s) {
   auto kern = dense_fwd_tc_kernel<MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
-  const long long total = (long long)a.B * (a.Hq / 16) * ((a.T + kTok - 1) / kTok);
+  const long long total = (long long)a.B * (a.Hq / 16) * ((a.Tq + kTok - 1) / kTok);
   const int grid = (int)(total < num_sms() ? total : num_sms());
   if (grid <= 0) return 0;
   kern<<<grid, kThreads, smem, s>>>(tmQ, tmK, tmV, a, pool_floats);

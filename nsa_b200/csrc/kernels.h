@@ -27,6 +27,7 @@ struct SelArgs {
   int accumulate;      // dq += instead of =
   int B, T, Hq, Hkv, S, BS;
   float scale;
+  int Tq, q0;          // queries are the tokens q0 .. q0+Tq-1 of the T-long sequence (q-indexed tensors hold Tq rows)
 };
 int launch_sel_fwd(const SelArgs& a, int D, cudaStream_t s);
 int launch_sel_dq(const SelArgs& a, int D, cudaStream_t s);
@@ -55,6 +56,7 @@ struct DenseArgs {
   int pool_k, pool_s, pool_p, n_pool;
   int* sel_idx;        // [B,T,Hq/16,n_sel] int32
   float* sel_scores;   // optional [B,Hq/16,T,n_pool] fp32 dump of the pooled scores, or null
+  int Tq, q0;          // query shard: q-indexed tensors hold Tq rows per batch, row i is sequence position q0+i
 };
 int launch_dense_fwd(const DenseArgs& a, int D, cudaStream_t s);
 int launch_dense_dq(const DenseArgs& a, int D, cudaStream_t s);
@@ -85,6 +87,7 @@ struct KvArgs {
   int B, T, Lk, Hq, Hk, BS, window;
   int cblock, cstride, causal;
   float scale;
+  int Tq, q0;             // query shard (rev_tok holds sequence positions)
 };
 int launch_kv_bwd(const KvArgs& a, int D, cudaStream_t s);
 int kv_status(int* out);
@@ -136,12 +139,13 @@ struct RevArgs {
   int* hist;      // workspace [B,H,NB(chunks),NB] int32
   int* rev_ptr;   // [B,H,NB+1]
   int* rev_tok;   // [B,H,cap]
-  long long cap;  // T*S
+  long long cap;  // Tq*S
+  int Tq, q0;     // query shard: idx/counts hold Tq rows per batch; T is the key sequence length
 };
 int launch_build_rev(const RevArgs& a, cudaStream_t s);
 // out(bf16)[i] = sum over valid segments of part[seg][i]
-int launch_reduce_segments(const float* part, bf16* out, int nseg, long long n_per_seg, int T, int Lk, int Hk, int D,
-                           int seg_len, int cblock, int cstride, int causal, cudaStream_t s);
+int launch_reduce_segments(const float* part, bf16* out, int nseg, long long n_per_seg, int q0, int Tq, int Lk, int Hk,
+                           int D, int seg_len, int cblock, int cstride, int causal, cudaStream_t s);
 int misc_status(int* out);
 
 int num_sms();

@@ -109,8 +109,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         st.list = a.rev_tok + (long long)bh * a.rev_cap;
       }
       if (a.window > 0) {
-        st.tb_lo = blk * 64;
-        st.nB = max(0, min(a.T, blk * 64 + 63 + a.window) - st.tb_lo);
+        st.tb_lo = max(blk * 64, a.q0);
+        st.nB = max(0, min(a.q0 + a.Tq, blk * 64 + 63 + a.window) - st.tb_lo);
       }
     } else {
       seg = (int)(item % a.nseg);
@@ -121,8 +121,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       b = bh / a.Hk;
       hk = bh % a.Hk;
       const int first = a.causal ? blk * 64 * a.cstride + a.cblock : 0;
-      st.ta_lo = max(first, seg * a.seg_len);
-      st.nA = min(a.T, (seg + 1) * a.seg_len) - st.ta_lo;
+      st.ta_lo = max(first, a.q0 + seg * a.seg_len);
+      st.nA = min(a.q0 + a.Tq, a.q0 + (seg + 1) * a.seg_len) - st.ta_lo;
       if (st.nA <= 0) skip = true;  // the reducer skips this segment too
     }
   }
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t q_s = ring + stage * STAGE, do_s = q_s + Q_TILE;
       // lanes 0-7 each issue the four boxes of their own token, so the issue latencies overlap
       if (lane < kTokB) {
-        const int qrow = (int)(((long long)b * a.T + tk) * a.Hq + hg * 16);
+        const int qrow = (int)(((long long)b * a.Tq + (tk - a.q0)) * a.Hq + hg * 16);
 #pragma unroll
         for (int p = 0; p < 2; ++p) {
           tma_load_2d(q_s + p * Q_PANEL + lane * 2048, &tmQ, fb, p * 64, qrow);
@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       r.gv = 1.f;
       if (n < nb) {
         const int sub = n / nb_sub;
-        const long long qrow = ((long long)b * a.T + t) * a.Hq + (hk * G16 + sub) * 16 + head;
+        const long long qrow = ((long long)b * a.Tq + (t - a.q0)) * a.Hq + (hk * G16 + sub) * 16 + head;
         r.lse2 = (br == 0 ? a.lse_a : a.lse_b)[qrow] * kLog2e;
         r.del = (br == 0 ? a.delta_a : a.delta_b)[qrow];
         const bf16* gp = br == 0 ? a.gate_a : a.gate_b;
@@ -391,7 +391,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 template <int MODE>
 int launch(const KvArgs& a, cudaStream_t s) {
   CUtensorMap tmQ, tmA, tmB, tmK, tmV;
-  const long long qrows = (long long)a.B * a.T * a.Hq;
+  const long long qrows = (long long)a.B * a.Tq * a.Hq;
   if (qrows > 0x7fffffffLL) {
     set_error("B*T*Hq exceeds the 2^31 rows a TMA coordinate can address");
     return -32;

@@ -84,6 +84,7 @@ __global__ void combine_kernel(const bf16* __restrict__ a0, const bf16* __restri
 // Replaces the dense boolean block mask of parallel_nsa_kernel_mask (nsa/selection_attn.py:256-273).
 // A stable counting sort by block id in three launches; the order inside every list is ascending in t and
 // independent of scheduling, so the backward is bit-reproducible.
+// `row` is the local (batch, token, head) row of idx/counts; `t` the token's sequence position
 __device__ __forceinline__ int rev_block(const RevArgs& a, long long row, int s, int t) {
   int cnt = a.S;
   if (a.counts) cnt = min(cnt, a.counts[row]);
@@ -103,24 +104,24 @@ __global__ void rev_hist_kernel(const RevArgs a) {
   __syncthreads();
   const int n = a.BS * a.S;
   for (int e = threadIdx.x; e < n; e += blockDim.x) {
-    const int t = chunk * a.BS + e / a.S, s = e % a.S;
-    if (t >= a.T) continue;
-    const int blk = rev_block(a, ((long long)b * a.T + t) * a.H + h, s, t);
+    const int tl = chunk * a.BS + e / a.S, s = e % a.S;
+    if (tl >= a.Tq) continue;
+    const int blk = rev_block(a, ((long long)b * a.Tq + tl) * a.H + h, s, a.q0 + tl);
     if (blk >= 0) atomicAdd(&sh[blk], 1);
   }
   __syncthreads();
-  int* out = a.hist + ((long long)bh * a.NB + chunk) * a.NB;
+  int* out = a.hist + ((long long)bh * gridDim.x + chunk) * a.NB;
   for (int i = threadIdx.x; i < a.NB; i += blockDim.x) out[i] = sh[i];
 }
 
 // grid (B*H): per block id, exclusive prefix over chunks (in place) and the CSR row pointers
-__global__ void rev_scan_kernel(const RevArgs a) {
+__global__ void rev_scan_kernel(const RevArgs a, const int nchunk) {
   extern __shared__ int tot[];
   const int bh = blockIdx.x;
-  int* hist = a.hist + (long long)bh * a.NB * a.NB;
+  int* hist = a.hist + (long long)bh * nchunk * a.NB;
   for (int blk = threadIdx.x; blk < a.NB; blk += blockDim.x) {
     int run = 0;
-    for (int c = 0; c < a.NB; ++c) {
+    for (int c = 0; c < nchunk; ++c) {
       const int v = hist[(long long)c * a.NB + blk];
       hist[(long long)c * a.NB + blk] = run;
       run += v;
@@ -146,14 +147,15 @@ __global__ void rev_fill_kernel(const RevArgs a) {
   const int b = bh / a.H, h = bh % a.H;
   const int lane = threadIdx.x;
   const int* rp = a.rev_ptr + (long long)bh * (a.NB + 1);
-  const int* pre = a.hist + ((long long)bh * a.NB + chunk) * a.NB;
+  const int* pre = a.hist + ((long long)bh * gridDim.x + chunk) * a.NB;
   for (int i = lane; i < a.NB; i += 32) cur[i] = rp[i] + pre[i];
   __syncwarp();
   int* out = a.rev_tok + (long long)bh * a.cap;
   for (int tt = 0; tt < a.BS; ++tt) {
-    const int t = chunk * a.BS + tt;
-    if (t >= a.T) break;
-    const long long row = ((long long)b * a.T + t) * a.H + h;
+    const int tl = chunk * a.BS + tt;
+    if (tl >= a.Tq) break;
+    const int t = a.q0 + tl;   // lists hold sequence positions
+    const long long row = ((long long)b * a.Tq + tl) * a.H + h;
     for (int s0 = 0; s0 < a.S; s0 += 32) {
       const int s = s0 + lane;
       const int blk = (s < a.S) ? rev_block(a, row, s, t) : -1;
@@ -173,7 +175,7 @@ __global__ void rev_fill_kernel(const RevArgs a) {
 
 // ---- fixed-order reduction of segment partials ----------------------------------------------------------
 __global__ void reduce_segments_kernel(const float* __restrict__ part, bf16* __restrict__ out, int nseg,
-                                       long long n_per_seg, int T, int Lk, int HkD, int seg_len, int cblock,
+                                       long long n_per_seg, int q0, int Tq, int Lk, int HkD, int seg_len, int cblock,
                                        int cstride, int causal) {
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
   if (i >= n_per_seg) return;
@@ -181,7 +183,7 @@ __global__ void reduce_segments_kernel(const float* __restrict__ part, bf16* __r
   const int first = causal ? (j / 64) * 64 * cstride + cblock : 0;
   float x = 0.f, y = 0.f;
   for (int seg = 0; seg < nseg; ++seg) {
-    const int lo = max(first, seg * seg_len), hi = min(T, (seg + 1) * seg_len);
+    const int lo = max(first, q0 + seg * seg_len), hi = min(q0 + Tq, q0 + (seg + 1) * seg_len);
     if (hi <= lo) continue;
     const float2 v = *reinterpret_cast<const float2*>(part + (long long)seg * n_per_seg + i);
     x += v.x;
@@ -228,7 +230,8 @@ int launch_build_rev(const RevArgs& a, cudaStream_t s) {
     set_error("reverse index: too many selection blocks (%d)", a.NB);
     return -34;
   }
-  const dim3 grid(a.NB, a.B * a.H);
+  const int nchunk = (a.Tq + a.BS - 1) / a.BS;   // chunks of BS local tokens
+  const dim3 grid(nchunk, a.B * a.H);
   const size_t sm = (size_t)a.NB * 4;
   if (sm > 48 * 1024) {
     cudaFuncSetAttribute(rev_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
@@ -236,17 +239,17 @@ int launch_build_rev(const RevArgs& a, cudaStream_t s) {
     cudaFuncSetAttribute(rev_fill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
   }
   rev_hist_kernel<<<grid, 128, sm, s>>>(a);
-  rev_scan_kernel<<<a.B * a.H, 256, sm, s>>>(a);
+  rev_scan_kernel<<<a.B * a.H, 256, sm, s>>>(a, nchunk);
   rev_fill_kernel<<<grid, 32, sm, s>>>(a);
   note_launches(3);
   return (int)cudaGetLastError();
 }
 
-int launch_reduce_segments(const float* part, bf16* out, int nseg, long long n_per_seg, int T, int Lk, int Hk, int D,
-                           int seg_len, int cblock, int cstride, int causal, cudaStream_t s) {
+int launch_reduce_segments(const float* part, bf16* out, int nseg, long long n_per_seg, int q0, int Tq, int Lk, int Hk,
+                           int D, int seg_len, int cblock, int cstride, int causal, cudaStream_t s) {
   if (n_per_seg <= 0) return 0;
   const long long pairs = n_per_seg / 2;
-  reduce_segments_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(part, out, nseg, n_per_seg, T, Lk, Hk * D,
+  reduce_segments_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(part, out, nseg, n_per_seg, q0, Tq, Lk, Hk * D,
                                                                           seg_len, cblock, cstride, causal);
   note_launches(1);
   return (int)cudaGetLastError();

@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kThreads, BWD ? 1 : 2)
 
   const int HG = a.Hq / 16;
   const int G16 = (a.Hq / a.Hkv) / 16;
-  const long long total = (long long)a.B * a.T * HG;
+  const long long total = (long long)a.B * a.Tq * HG;
 
   if (warp == kConsumerWarps) {
     // ------------------------------- producer ------------------------------------------------
@@ -71,9 +71,9 @@ __global__ void __launch_bounds__(kThreads, BWD ? 1 : 2)
     // the first 32 indices of the next item are fetched while the current item's gathers are issued
     auto item_row = [&](long long item) {
       const int hg = (int)(item % HG);
-      const int t = a.T - 1 - (int)((item / HG) % a.T);
-      const int b = (int)(item / ((long long)HG * a.T));
-      return ((long long)b * a.T + t) * a.Hkv + hg / G16;
+      const int tl = a.Tq - 1 - (int)((item / HG) % a.Tq);
+      const int b = (int)(item / ((long long)HG * a.Tq));
+      return ((long long)b * a.Tq + tl) * a.Hkv + hg / G16;
     };
     auto fetch = [&](long long item, int& cnt, int& first) {
       cnt = 0;
@@ -88,10 +88,11 @@ __global__ void __launch_bounds__(kThreads, BWD ? 1 : 2)
     fetch(blockIdx.x, cnt_next, first_next);
     for (long long item = blockIdx.x; item < total; item += gridDim.x) {
       const int hg = (int)(item % HG);
-      const int t = a.T - 1 - (int)((item / HG) % a.T);
-      const int b = (int)(item / ((long long)HG * a.T));
+      const int tl = a.Tq - 1 - (int)((item / HG) % a.Tq);
+      const int t = a.q0 + tl;   // sequence position of this query
+      const int b = (int)(item / ((long long)HG * a.Tq));
       const int hkv = hg / G16;
-      const long long row = ((long long)b * a.T + t) * a.Hkv + hkv;
+      const long long row = ((long long)b * a.Tq + tl) * a.Hkv + hkv;
       const int cnt = cnt_next, first = first_next;
       fetch(item + gridDim.x, cnt_next, first_next);
       for (int s0 = 0; s0 < cnt; s0 += 32) {
@@ -136,11 +137,12 @@ __global__ void __launch_bounds__(kThreads, BWD ? 1 : 2)
   uint32_t it = 0;
   for (long long item = blockIdx.x; item < total; item += gridDim.x) {
     const int hg = (int)(item % HG);
-    const int t = a.T - 1 - (int)((item / HG) % a.T);
-    const int b = (int)(item / ((long long)HG * a.T));
+    const int tl = a.Tq - 1 - (int)((item / HG) % a.Tq);
+    const int t = a.q0 + tl;   // sequence position of this query
+    const int b = (int)(item / ((long long)HG * a.Tq));
     const int hkv = hg / G16;
-    const long long row = ((long long)b * a.T + t) * a.Hkv + hkv;
-    const long long qrow = ((long long)b * a.T + t) * a.Hq + hg * 16;  // first of the 16 (token, head) rows
+    const long long row = ((long long)b * a.Tq + tl) * a.Hkv + hkv;
+    const long long qrow = ((long long)b * a.Tq + tl) * a.Hq + hg * 16;  // first of the 16 (token, head) rows
 
     uint32_t qf[D / 16][4];
     load_a_frags_global<D>(qf, a.q + qrow * D, lane);
@@ -337,7 +339,7 @@ int launch(const SelArgs& a, cudaStream_t s) {
   auto kern = sel_qmajor_kernel<D, BWD>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
-  const long long total = (long long)a.B * a.T * (a.Hq / 16);
+  const long long total = (long long)a.B * a.Tq * (a.Hq / 16);
   const long long slots = (long long)num_sms() * (BWD ? 1 : 2);
   const int grid = (int)(total < slots ? total : slots);
   if (grid <= 0) return 0;

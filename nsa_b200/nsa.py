@@ -15,11 +15,13 @@ class _NSACore(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, ck, cv, g_slc, g_swa, g_cmp, cfg):
-        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window) = cfg
+        """q, gates: [B,Tq,Hq,(D)] = the queries at sequence positions q0 .. q0+Tq-1; k, v: [B,T,Hkv,D] and ck, cv:
+        [B,Tc,Hkv,D] cover the whole sequence.  cfg[-1] = q0 (0 and Tq == T for an unsharded call)."""
+        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window, q0) = cfg
         q, k, v, ck, cv = (_lib.require(t, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (ck, "ck"), (cv, "cv")))
         g_slc, g_swa, g_cmp = (_lib.require(t, "gate") for t in (g_slc, g_swa, g_cmp))
-        B, T, Hq, D = q.shape
-        Hkv, Tc = k.shape[2], ck.shape[1]
+        B, Tq, Hq, D = q.shape
+        T, Hkv, Tc = k.shape[1], k.shape[2], ck.shape[1]
         L, P, S = _lib.lib(), _lib.ptr, _lib.stream
         dev = q.device
         n_pool = L.nsa_pool_out_len(Tc, pool_k, pool_s, pool_p)
@@ -27,15 +29,15 @@ class _NSACore(torch.autograd.Function):
             raise RuntimeError("selected index k out of range: %d blocks requested, %d exist" % (n_sel, n_pool))
         o_cmp, o_slc, o = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
         o_swa = torch.empty_like(q) if window > 0 else None
-        lse_cmp, lse_slc = (torch.empty(B, T, Hq, dtype=torch.float32, device=dev) for _ in range(2))
+        lse_cmp, lse_slc = (torch.empty(B, Tq, Hq, dtype=torch.float32, device=dev) for _ in range(2))
         lse_swa = torch.empty_like(lse_slc) if window > 0 else None
-        idx = torch.empty(B, T, Hkv, n_sel, dtype=torch.int32, device=dev)
-        _lib.check(L.nsa_cmp_attn_fwd(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, B, T, Tc, Hq, Hkv, D, block,
-                                      stride, 1 if causal else 0, scale, n_sel, pool_k, pool_s, pool_p, S()),
-                   "nsa_cmp_attn_fwd")
-        _lib.check(L.nsa_sel_swa_fwd(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(lse_slc), P(o_swa), P(lse_swa),
-                                     P(g_slc), P(g_swa), P(o_cmp), P(g_cmp), P(o), B, T, Hq, Hkv, D, n_sel, sel_block,
-                                     window, scale, S()), "nsa_sel_swa_fwd")
+        idx = torch.empty(B, Tq, Hkv, n_sel, dtype=torch.int32, device=dev)
+        _lib.check(L.nsa_cmp_attn_fwd_sharded(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, B, T, Tc, Hq, Hkv,
+                                              D, block, stride, 1 if causal else 0, scale, n_sel, pool_k, pool_s, pool_p,
+                                              Tq, q0, S()), "nsa_cmp_attn_fwd")
+        _lib.check(L.nsa_sel_swa_fwd_sharded(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(lse_slc), P(o_swa),
+                                             P(lse_swa), P(g_slc), P(g_swa), P(o_cmp), P(g_cmp), P(o), B, T, Hq, Hkv, D,
+                                             n_sel, sel_block, window, scale, Tq, q0, S()), "nsa_sel_swa_fwd")
         ctx.save_for_backward(q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx)
         ctx.cfg = cfg
         return o
@@ -43,16 +45,16 @@ class _NSACore(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do):
         (q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx) = ctx.saved_tensors
-        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window) = ctx.cfg
+        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window, q0) = ctx.cfg
         do = _lib.require(do, "do")
-        B, T, Hq, D = q.shape
-        Hkv, Tc = k.shape[2], ck.shape[1]
+        B, Tq, Hq, D = q.shape
+        T, Hkv, Tc = k.shape[1], k.shape[2], ck.shape[1]
         L, P, S = _lib.lib(), _lib.ptr, _lib.stream
         dev = q.device
-        rows = B * T * Hq
+        rows = B * Tq * Hq
 
         def delta_and_dgate(o_x, g_x):
-            delta = torch.empty(B, T, Hq, dtype=torch.float32, device=dev)
+            delta = torch.empty(B, Tq, Hq, dtype=torch.float32, device=dev)
             dg = torch.empty_like(g_x)
             _lib.check(L.nsa_rowdot(P(o_x), P(do), P(g_x), P(delta), P(dg), rows, D, S()), "nsa_rowdot")
             return delta, dg
@@ -63,16 +65,16 @@ class _NSACore(torch.autograd.Function):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         ws_bytes = L.nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, n_sel, sel_block)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        _lib.check(L.nsa_sel_swa_bwd(P(q), P(k), P(v), P(idx), 0, None, P(do), P(lse_slc), P(delta_slc), P(g_slc),
-                                     P(do) if window > 0 else None, P(lse_swa), P(delta_swa), P(g_swa), P(dq), 0, P(dk),
-                                     P(dv), P(ws), ws_bytes, B, T, Hq, Hkv, D, n_sel, sel_block, window, scale, S()),
-                   "nsa_sel_swa_bwd")
+        _lib.check(L.nsa_sel_swa_bwd_sharded(P(q), P(k), P(v), P(idx), 0, None, P(do), P(lse_slc), P(delta_slc), P(g_slc),
+                                             P(do) if window > 0 else None, P(lse_swa), P(delta_swa), P(g_swa), P(dq), 0,
+                                             P(dk), P(dv), P(ws), ws_bytes, B, T, Hq, Hkv, D, n_sel, sel_block, window,
+                                             scale, Tq, q0, S()), "nsa_sel_swa_bwd")
         dck, dcv = torch.empty_like(ck), torch.empty_like(cv)
         ws_bytes = L.nsa_cmp_attn_bwd_workspace_bytes(B, T, Tc, Hkv, D)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        _lib.check(L.nsa_cmp_attn_bwd(P(q), P(ck), P(cv), P(lse_cmp), P(do), P(delta_cmp), P(g_cmp), P(dq), 1, P(dck),
-                                      P(dcv), P(ws), ws_bytes, B, T, Tc, Hq, Hkv, D, block, stride, 1 if causal else 0,
-                                      scale, S()), "nsa_cmp_attn_bwd")
+        _lib.check(L.nsa_cmp_attn_bwd_sharded(P(q), P(ck), P(cv), P(lse_cmp), P(do), P(delta_cmp), P(g_cmp), P(dq), 1,
+                                              P(dck), P(dcv), P(ws), ws_bytes, B, T, Tc, Hq, Hkv, D, block, stride,
+                                              1 if causal else 0, scale, Tq, q0, S()), "nsa_cmp_attn_bwd")
         return dq, dk, dv, dck, dcv, dg_slc, dg_swa, dg_cmp, None
 
 
@@ -150,6 +152,6 @@ class NSAAttention(nn.Module):
         v4 = v.reshape(bs, -1, num_kv_head, head_v_dim)
         cfg = (self.compression_stride, self.compression_block, bool(causal), float(scale), self.pool_kernel_size,
                self.pool_stride, self.pool_padding, self.selected_block_count, self.selection_block_size,
-               self.sliding_window)
+               self.sliding_window, 0)
         o = _NSACore.apply(q4, k4, v4, ck, cv, g_slc, g_swa, g_cmp, cfg)
         return o.reshape(-1, *o.shape[-2:])

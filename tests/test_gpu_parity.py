@@ -384,3 +384,43 @@ def test_selection_full_size_properties(nsa):
                                       idx[b:b + 1, t:t + 1].cpu().long(), None, BS, q_pos=torch.tensor([t]))
         _close("row (%d,%d)" % (b, t), o[b, t], ref[0, 0])
     nsa._lib.device_status()
+
+
+# ------------------------------------------------------------------------------------------------------
+# query shards (context parallelism): the kernels run on a slice of the queries against the whole K/V
+# ------------------------------------------------------------------------------------------------------
+def test_query_shards_match_unsharded_run(nsa):
+    """Emulates 2 ranks with the zig-zag layout on one GPU: four query chunks run one after the other through the
+    sharded entry points; outputs, selected indices and dQ must equal the unsharded run, dK/dV/dCK/dCV must sum to it."""
+    from nsa_b200.nsa import _NSACore
+    gen = torch.Generator().manual_seed(77)
+    B, T, Hq, Hkv, D, n_sel, window = 1, 1024, 32, 2, 128, 4, 128
+    Tc = (T - 32) // 16 + 1
+    q, k, v = (_dev(_r(torch.randn(B, T, h, D, generator=gen))) for h in (Hq, Hkv, Hkv))
+    ck, cv = (_dev(_r(torch.randn(B, Tc, Hkv, D, generator=gen) * 0.5)) for _ in range(2))
+    gates = [_dev(_r(torch.rand(B, T, Hq, generator=gen))) for _ in range(3)]
+    do = _dev(_r(torch.randn(B, T, Hq, D, generator=gen)))
+
+    def run(q0, Tq):
+        sl = slice(q0, q0 + Tq)
+        leaves = [t.clone().requires_grad_(True) for t in (q[:, sl].contiguous(), k, v, ck, cv)]
+        g = [x[:, sl].contiguous() for x in gates]
+        cfg = (16, 32, True, D ** -0.5, 5, 4, 0, n_sel, 64, window, q0)
+        o = _NSACore.apply(*leaves, *g, cfg)
+        o.backward(do[:, sl].contiguous())
+        return o.detach(), [t.grad for t in leaves]
+
+    o_full, g_full = run(0, T)
+    chunk = T // 4
+    o_parts, dq_parts = {}, {}
+    sums = [torch.zeros_like(t, dtype=torch.float32) for t in g_full[1:]]
+    for cid in (0, 3, 1, 2):                      # rank 0 owns chunks 0 and 3, rank 1 owns 1 and 2
+        o, grads = run(cid * chunk, chunk)
+        o_parts[cid], dq_parts[cid] = o, grads[0]
+        for s_, g_ in zip(sums, grads[1:]):
+            s_ += g_.float()
+    assert torch.equal(torch.cat([o_parts[c] for c in range(4)], 1), o_full)
+    assert torch.equal(torch.cat([dq_parts[c] for c in range(4)], 1), g_full[0])
+    for name, s_, ref in zip(("dk", "dv", "dck", "dcv"), sums, g_full[1:]):
+        _close(name + " summed over shards", s_, ref, scaled=True)
+    nsa._lib.device_status()
