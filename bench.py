@@ -421,6 +421,82 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_context(args):
+    """BASELINE configs[3]: one sequence of 65536 tokens, fwd+bwd, context-sharded over the ranks (zig-zag chunks,
+    NCCL all-gather of K/V, reduce-scatter of dK/dV, all-reduce of the weight gradients).  N=1 is the scaling base."""
+    import torch
+    import torch.distributed as dist
+    import nsa_b200
+    from nsa_b200 import _lib
+    from nsa_b200.context_parallel import context_parallel_forward
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    c = dict(CFG, B=1, T=65536, seed=3)
+    T, Hq, Hkv, D = c["T"], c["Hq"], c["Hkv"], c["D"]
+    Tl = T // world
+    gen = torch.Generator().manual_seed(c["seed"] * 1000 + rank)
+    q, k, v, do = (torch.randn(1, Tl, h, D, generator=gen).to(dev, torch.bfloat16) for h in (Hq, Hkv, Hkv, Hq))
+    wgen = torch.Generator().manual_seed(c["seed"])
+    mod = nsa_b200.NSAAttention(D, True, None, 0.0, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.copy_(torch.randn(p.shape, generator=wgen) * 0.02)
+    params = list(mod.parameters())
+    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+
+    def step():
+        for t in [q, k, v] + params:
+            t.grad = None
+        if world == 1:
+            o = mod(q.view(T, Hq, D), k.view(T, Hkv, D), v.view(T, Hkv, D), cu, T)
+            o.backward(do.view(T, Hq, D))
+        else:
+            o = context_parallel_forward(mod, q, k, v, None, zigzag=True)
+            o.backward(do)
+            flat = torch.cat([p.grad.reshape(-1) for p in params])
+            dist.all_reduce(flat)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms.item()) / args.steps
+    _lib.device_status()
+    if rank == 0:
+        fm = flop_model(1, T, Hq, Hkv, D, c["block"], c["stride"], c["sel_block"], c["n_sel"], c["window"])
+        print(json.dumps({
+            "metric": METRIC, "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[3]: NSAAttention fwd+bwd bf16, B=1 T=65536 Hq=64 Hkv=4 D=128, context-sharded "
+                                   "(zig-zag chunks, NCCL all-gather of K/V, reduce-scatter of dK/dV)",
+                       "parallelism": "context-sharded x%d" % world},
+            "tflops_algorithmic": fm["total"] / (ms_step * 1e-3) / 1e12}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_profile_case():
     """B=1 slice of the workload (q, dO 134 MB each: larger than L2, well under 1 GB on the device)."""
     import torch
@@ -446,6 +522,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="module", choices=["module", "context"],
+                    help="module: configs[2], batch-sharded (default).  context: configs[3], B=1 T=65536 context-sharded")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for ncu: B=1 of the workload, every kernel family launched twice, no timing loop")
     args = ap.parse_args()
@@ -453,6 +531,8 @@ def main():
         run_reference(args)
     elif args.profile_case:
         run_profile_case()
+    elif args.workload == "context":
+        run_context(args)
     else:
         run_gpu(args)
 

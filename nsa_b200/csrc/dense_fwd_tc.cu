@@ -31,7 +31,7 @@ constexpr uint32_t TILE = 2 * PANEL;          // 32 KB
 constexpr uint32_t STAGE = 2 * TILE;          // K + V
 constexpr int kStages = 2;
 constexpr uint32_t kTmemCols = 512;           // S0 0..127, S1 128..255, O 256..383
-constexpr int kMaxPool = 512;
+constexpr int kMaxPool = 1024;
 
 struct Sched {
   int first, nA, nAttn, nB;
@@ -62,7 +62,8 @@ __device__ __forceinline__ Sched make_sched(const DenseArgs& a, int t0) {
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
     dense_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                        const __grid_constant__ CUtensorMap tmV, const DenseArgs a, const int pool_floats) {
+                        const __grid_constant__ CUtensorMap tmV, const DenseArgs a, const int pool_floats,
+                        const int smem_bytes) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sbase = (raw + 1023u) & ~1023u;
@@ -75,8 +76,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                  s_free0 = misc + 64, p_full = misc + 80, p_free = misc + 88, o_full = misc + 96, tmem_slot = misc + 104, o_free = misc + 120;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + (misc - sbase) + 112);
   float* xch = reinterpret_cast<float*>(sgen + (misc - sbase) + 128);  // [2 parity][2 half][128 rows]
-  float* xst = xch + 2 * 2 * 128;                                       // [2 values][2 half][128 rows]
-  float* pool = xst + 2 * 2 * 128;                                      // [kTok][pool_floats]
+  float* xst = xch;                                                     // statistics merge reuses it (see below)
+  float* pool = xch + 2 * 2 * 128;                                      // [kTok][pool_floats]
+  // the layout must fit behind the 1024-byte round-up of the base (the host leaves less slack for long sequences)
+  if ((misc - raw) + 128 + 2 * 2 * 128 * 4 + kTok * pool_floats * 4 > (uint32_t)smem_bytes) {
+    if (threadIdx.x == 0) atomicCAS(&g_dev_error, 0, DEV_ERR_BOUNDS);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -242,7 +248,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int j0 = jt * 128 + half * 64;     // first key column of this thread
         const uint32_t st = c & 1;
         if (do_sel && i == sc.nA) {
-          // merge the two halves' raw-score statistics before the second pass
+          // merge the two halves' raw-score statistics before the second pass (the exchange buffer is shared with
+          // the per-tile maxima: wait until nobody reads those any more)
+          named_bar_sync(1, kSoft);
           xst[(0 * 2 + half) * 128 + row] = m2;
           xst[(1 * 2 + half) * 128 + row] = l2;
           named_bar_sync(1, kSoft);
@@ -522,14 +530,23 @@ int launch(const DenseArgs& a, cudaStream_t s) {
   if (rc) return rc;
   const bool sel = MODE == 1 && a.n_sel > 0;
   const int pool_floats = sel ? (a.n_pool + 3) / 4 * 4 : 0;
-  const int smem = (int)(TILE + kStages * STAGE + TILE) + 128 + 2 * (2 * 2 * 128 * 4) + kTok * pool_floats * 4 + 1024;
+  const int need = (int)(TILE + kStages * STAGE + TILE) + 128 + 2 * 2 * 128 * 4 + kTok * pool_floats * 4;
+  int dev = 0, max_smem = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  int smem = need + 1024;                      // room for rounding the base up to 1024 bytes
+  if (smem > max_smem) smem = max_smem;        // long sequences: less slack (the kernel checks that it still fits)
+  if (smem < need + 128) {
+    set_error("dense attention: the pooled-score vector (n_pool=%d) does not fit in shared memory", a.n_pool);
+    return -31;
+  }
   auto kern = dense_fwd_tc_kernel<MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
   const long long total = (long long)a.B * (a.Hq / 16) * ((a.Tq + kTok - 1) / kTok);
   const int grid = (int)(total < num_sms() ? total : num_sms());
   if (grid <= 0) return 0;
-  kern<<<grid, kThreads, smem, s>>>(tmQ, tmK, tmV, a, pool_floats);
+  kern<<<grid, kThreads, smem, s>>>(tmQ, tmK, tmV, a, pool_floats, smem);
   note_launches(1);
   return (int)cudaGetLastError();
 }
