@@ -497,6 +497,86 @@ def run_context(args):
         dist.destroy_process_group()
 
 
+def run_decode(args):
+    """BASELINE configs[4]: 128 sequences with KV lengths uniform in [4096, 32768] (seed 4), one new query token each;
+    sequences are assigned to the ranks by longest-processing-time bin packing (work ~ L); no collective."""
+    import torch
+    import torch.distributed as dist
+    import nsa_b200
+    from nsa_b200 import _lib
+    from nsa_b200.decode import compress_cache, nsa_decode
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    c = CFG
+    Hq, Hkv, D = c["Hq"], c["Hkv"], c["D"]
+    lens = torch.randint(4096, 32769, (128,), generator=torch.Generator().manual_seed(4)).tolist()
+    bins = [[] for _ in range(world)]
+    load = [0] * world
+    for i in sorted(range(128), key=lambda i: -lens[i]):
+        r = load.index(min(load))
+        bins[r].append(i)
+        load[r] += lens[i]
+    mine = [lens[i] for i in bins[rank]]
+    cu = [0]
+    for n in mine:
+        cu.append(cu[-1] + n)
+    gen = torch.Generator().manual_seed(4000 + rank)
+    q = torch.randn(len(mine), Hq, D, generator=gen).to(dev, torch.bfloat16)
+    k = torch.randn(cu[-1], Hkv, D, generator=gen).to(dev, torch.bfloat16)
+    v = torch.randn(cu[-1], Hkv, D, generator=gen).to(dev, torch.bfloat16)
+    mod = nsa_b200.NSAAttention(D, True, None, 0.0, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.copy_(torch.randn(p.shape, generator=torch.Generator().manual_seed(4)) * 0.02)
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / args.steps
+
+    with torch.no_grad():
+        ms_stateless = timed(lambda: nsa_decode(mod, q, k, v, cu))
+        cache = compress_cache(mod, k, v, cu)
+        ms_cached = timed(lambda: nsa_decode(mod, q, k, v, cu, cache=cache))
+    _lib.device_status()
+    if rank == 0:
+        peaks = read_peaks()
+        kv_bytes = sum(lens) * Hkv * D * 2 * 2
+        print(json.dumps({
+            "metric": "NSA decode tokens/s (one new token per sequence)", "value": 128 / (ms_stateless * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_stateless,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[4]: varlen decode, 128 sequences, KV length U[4096,32768] seed 4, Hq=64 Hkv=4 "
+                                   "D=128; stateless (re-compresses the whole cache every step)",
+                       "parallelism": "sequence-sharded x%d (LPT)" % world, "sum_kv_len": sum(lens)},
+            "with_compressed_cache": {"ms_per_step": ms_cached, "tokens_per_s": 128 / (ms_cached * 1e-3)},
+            "roofline": {"bound": "hbm", "achieved": round(kv_bytes / (ms_stateless * 1e-3) / 1e9 / world, 1),
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s per GPU",
+                         "frac": round(kv_bytes / (ms_stateless * 1e-3) / 1e9 / world / peaks["hbm_gbs"], 4),
+                         "traffic": None, "algorithmic_bytes": kv_bytes}}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_profile_case():
     """B=1 slice of the workload (q, dO 134 MB each: larger than L2, well under 1 GB on the device)."""
     import torch
@@ -522,7 +602,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="module", choices=["module", "context"],
+    ap.add_argument("--workload", default="module", choices=["module", "context", "decode"],
                     help="module: configs[2], batch-sharded (default).  context: configs[3], B=1 T=65536 context-sharded")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for ncu: B=1 of the workload, every kernel family launched twice, no timing loop")
@@ -533,6 +613,8 @@ def main():
         run_profile_case()
     elif args.workload == "context":
         run_context(args)
+    elif args.workload == "decode":
+        run_decode(args)
     else:
         run_gpu(args)
 

@@ -136,6 +136,18 @@ int nsa_sel_swa_bwd_sharded(const void* q, const void* k, const void* v, const v
                             size_t ws_bytes, int B, int T, int Hq, int Hkv, int D, int S, int BS, int window,
                             float scale, int Tq, int q0, void* stream);
 
+/* ---- decode ---------------------------------------------------------------------------------------------
+ * No entry point of the reference does this (its module assumes len(q) == len(k), nsa/nsa.py:97); it is the
+ * module's forward (nsa/nsa.py:94-135) for ONE new query token per sequence, at position L-1 of a packed
+ * K/V cache.  q, o and the scratch o_cmp / o_slc / o_swa [nseq,Hq,D]; k, v [sum L,Hkv,D]; ck, cv
+ * [sum Tc,Hkv,D] = the compressed cache (nsa_compress_fwd with the Conv1d length rule); cu_k, cu_c: HOST int32
+ * [nseq+1]; gates [nseq,Hq] (NULL = 1); lse fp32 [3,nseq,Hq] and idx int32 [nseq,Hkv,n_sel] receive the
+ * branch log-sum-exps and the selected blocks.  Needs head_dim 128, 64-key blocks, stride 16 / block 32. */
+int nsa_decode_fwd(const void* q, const void* k, const void* v, const void* ck, const void* cv, const int32_t* cu_k,
+                   const int32_t* cu_c, const void* g_slc, const void* g_swa, const void* g_cmp, void* o, void* o_cmp,
+                   void* o_slc, void* o_swa, float* lse, int32_t* idx, int nseq, int Hq, int Hkv, int D, int block,
+                   int stride, int sel_block, int n_sel, int window, float scale, void* stream);
+
 /* ---- helpers --------------------------------------------------------------------------------------
  * delta[r] = (gate ? gate[r] : 1) * sum_d o[r,d]*dout[r,d] (fp32, NULL to skip) and
  * dgate[r] = sum_d o[r,d]*dout[r,d] (bf16, NULL to skip); rows = B*T*Hq.

@@ -409,6 +409,40 @@ int nsa_sel_swa_bwd_sharded(const void* q, const void* k, const void* v, const v
   return sel_swa_bwd_impl(q, k, v, idx, idx64, counts, dout_slc, lse_slc, delta_slc, gate_slc, dout_swa, lse_swa, delta_swa, gate_swa, dq, accumulate_dq, dk, dv, ws, ws_bytes, B, T, Hq, Hkv, D, S, BS, window, scale, Tq, q0, stream);
 }
 
+// ---- decode ---------------------------------------------------------------------------------------------
+int nsa_decode_fwd(const void* q, const void* k, const void* v, const void* ck, const void* cv, const int32_t* cu_k,
+                   const int32_t* cu_c, const void* g_slc, const void* g_swa, const void* g_cmp, void* o, void* o_cmp,
+                   void* o_slc, void* o_swa, float* lse, int32_t* idx, int nseq, int Hq, int Hkv, int D, int block,
+                   int stride, int sel_block, int n_sel, int window, float scale, void* stream) {
+  if (!q || !k || !v || !ck || !cv || !cu_k || !cu_c || !o || !o_cmp || !o_slc || !lse || !idx)
+    return fail(-1, "nsa_decode_fwd: null pointer");
+  if (window > 0 && !o_swa) return fail(-1, "nsa_decode_fwd: o_swa is null");
+  if (nseq <= 0) return 0;
+  const int pool_k = sel_block / stride + 1, pool_s = sel_block / stride, pool_p = block / stride - 2;
+  const bf16 *qb = (const bf16*)q, *kb = (const bf16*)k, *vb = (const bf16*)v, *ckb = (const bf16*)ck, *cvb = (const bf16*)cv;
+  const bf16 *gs = (const bf16*)g_slc, *gw = (const bf16*)g_swa, *gc = (const bf16*)g_cmp;
+  for (int i = 0; i < nseq; ++i) {
+    const int L = cu_k[i + 1] - cu_k[i], Tc = cu_c[i + 1] - cu_c[i];
+    if (L <= 0 || Tc <= 0) return fail(-13, "nsa_decode_fwd: sequence %d is shorter than one compression block", i);
+    const long long qo = (long long)i * Hq * D, ro = (long long)i * Hq;
+    const bf16* ki = kb + (long long)cu_k[i] * Hkv * D;
+    const bf16* vi = vb + (long long)cu_k[i] * Hkv * D;
+    const bf16* cki = ckb + (long long)cu_c[i] * Hkv * D;
+    const bf16* cvi = cvb + (long long)cu_c[i] * Hkv * D;
+    int32_t* idx_i = idx + (long long)i * Hkv * n_sel;
+    // the newest token (position L-1) is the only query: a one-row query shard of the sequence
+    int rc = cmp_attn_fwd_impl(qb + qo, cki, cvi, (bf16*)o_cmp + qo, lse + ro, idx_i, nullptr, 1, L, Tc, Hq, Hkv, D, block,
+                               stride, 1, scale, n_sel, pool_k, pool_s, pool_p, 1, L - 1, stream);
+    if (rc) return rc;
+    rc = sel_swa_fwd_impl(qb + qo, ki, vi, idx_i, 0, nullptr, (bf16*)o_slc + qo, lse + (long long)nseq * Hq + ro,
+                          window > 0 ? (bf16*)o_swa + qo : nullptr, lse + 2ll * nseq * Hq + ro, gs ? gs + ro : nullptr,
+                          gw ? gw + ro : nullptr, (bf16*)o_cmp + qo, gc ? gc + ro : nullptr, (bf16*)o + qo, 1, L, Hq, Hkv,
+                          D, n_sel, sel_block, window, scale, 1, L - 1, stream);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
 // ---- helpers ------------------------------------------------------------------------------------------
 int nsa_rowdot(const void* o, const void* dout, const void* gate, float* delta, void* dgate, long long rows, int D,
                void* stream) {

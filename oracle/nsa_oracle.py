@@ -289,7 +289,7 @@ def nsa_forward(q, k, v, wk, bk, wv, bv, wg, bg, *, stride=16, block=32, sel_blo
 
 
 def nsa_decode_row(q_row, k, v, wk, bk, wv, bv, wg, bg, *, stride=16, block=32, sel_block=64,
-                   n_sel=16, window=512, scale=None):
+                   n_sel=16, window=512, scale=None, ck=None, cv=None, return_scores=False):
     """The module's output for the single query at position t = L-1 of one sequence, given that
     sequence's whole K/V.  q_row [Hq,D]; k,v [L,Hkv,D].  The same formulas as ``nsa_forward``
     evaluated for the last row only (the reference has no decode entry point; its module
@@ -301,8 +301,10 @@ def nsa_decode_row(q_row, k, v, wk, bk, wv, bv, wg, bg, *, stride=16, block=32, 
     if scale is None:
         scale = D ** -0.5
     qf = q_row.float()
-    ck = compress_conv(k.unsqueeze(0), wk, bk, block, stride)[0]           # [Tc,Hkv,D]
-    cv = compress_conv(v.unsqueeze(0), wv, bv, block, stride)[0]
+    if ck is None:   # (a caller may pass the compressed cache it wants the row evaluated on)
+        ck = compress_conv(k.unsqueeze(0), wk, bk, block, stride)[0]       # [Tc,Hkv,D]
+        cv = compress_conv(v.unsqueeze(0), wv, bv, block, stride)[0]
+    ck, cv = ck.float(), cv.float()
     Tc = ck.shape[0]
     ckr, cvr = ck.repeat_interleave(G, 1), cv.repeat_interleave(G, 1)      # [Tc,Hq,D]
     raw = torch.einsum("hd,shd->hs", qf, ckr)
@@ -332,6 +334,8 @@ def nsa_decode_row(q_row, k, v, wk, bk, wv, bv, wg, bg, *, stride=16, block=32, 
     o_swa = torch.einsum("hs,shd->hd", torch.softmax(ss, -1), v[k0:].float().repeat_interleave(G, 1))
     gate = qf @ wg.float().t() + bg.float()
     o = o_slc * gate[:, 0:1] + o_swa * gate[:, 1:2] + o_cmp * gate[:, 2:3]
+    if return_scores:
+        return o, idx, sc
     return o, idx
 
 

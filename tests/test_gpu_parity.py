@@ -424,3 +424,41 @@ def test_query_shards_match_unsharded_run(nsa):
     for name, s_, ref in zip(("dk", "dv", "dck", "dcv"), sums, g_full[1:]):
         _close(name + " summed over shards", s_, ref, scaled=True)
     nsa._lib.device_status()
+
+
+def test_decode_rows_match_oracle(nsa):
+    """One new token per sequence against a packed K/V cache of ragged lengths (BASELINE config 5's shape in small)."""
+    from nsa_b200.decode import compress_cache, nsa_decode
+    gen = torch.Generator().manual_seed(404)
+    Hq, Hkv, D, n_sel, window = 32, 2, 128, 3, 64
+    lens = [300, 1061, 2048, 517]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    q = _r(torch.randn(len(lens), Hq, D, generator=gen))
+    k = _r(torch.randn(cu[-1], Hkv, D, generator=gen))
+    v = _r(torch.randn(cu[-1], Hkv, D, generator=gen))
+    mod = nsa.NSAAttention(D, True, selected_block_count=n_sel, sliding_window=window, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.copy_(_r(torch.randn(p.shape, generator=gen) * 0.02))
+        mod.gating.bias.copy_(_r(torch.tensor([0.5, 0.4, 0.6])))
+    kd, vd = _dev(k), _dev(v)
+    cache = compress_cache(mod, kd, vd, cu)
+    o = nsa_decode(mod, _dev(q), kd, vd, cu, cache=cache)
+    o2 = nsa_decode(mod, _dev(q), kd, vd, torch.tensor(cu, dtype=torch.int32, device=DEV))   # re-compressing path
+    assert torch.equal(o, o2)
+    ck, cv, _, cu_c = cache
+    wk, bk = (t.detach().float().cpu() for t in (mod.compressor.compressor_k.weight, mod.compressor.compressor_k.bias))
+    wv, bv = (t.detach().float().cpu() for t in (mod.compressor.compressor_v.weight, mod.compressor.compressor_v.bias))
+    wg, bg = mod.gating.weight.detach().float().cpu(), mod.gating.bias.detach().float().cpu()
+    for i, L in enumerate(lens):
+        ks, vs = k[cu[i]:cu[i + 1]], v[cu[i]:cu[i + 1]]
+        _close("ck of sequence %d" % i, ck[cu_c[i]:cu_c[i + 1]], O.compress_conv(ks.unsqueeze(0), wk, bk, 32, 16)[0])
+        # the row itself, evaluated by the oracle on the kernel's compressed cache (bf16) so that near-tie selections
+        # do not confound the comparison; gates as the bf16 tensors the module produces
+        ref, ref_idx, sc = O.nsa_decode_row(q[i], ks, vs, wk, bk, wv, bv, wg, bg, n_sel=n_sel, window=window,
+                                            ck=ck[cu_c[i]:cu_c[i + 1]].cpu(), cv=cv[cu_c[i]:cu_c[i + 1]].cpu(),
+                                            return_scores=True)
+        _close("decode row %d" % i, o[i], ref, atol=3e-2)
+    nsa._lib.device_status()
