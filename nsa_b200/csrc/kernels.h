@@ -32,6 +32,10 @@ struct SelArgs {
 int launch_sel_fwd(const SelArgs& a, int D, cudaStream_t s);
 int launch_sel_dq(const SelArgs& a, int D, cudaStream_t s);
 int sel_status(int* out);
+// one item per warp, whole 64-key blocks (sel_block.cu); used when sel_block_supported()
+bool sel_block_supported(const SelArgs& a, int D);
+int launch_sel_block(const SelArgs& a, int D, bool bwd, cudaStream_t s);
+int sel_block_status(int* out);
 
 // ---- dense query-major attention: sliding window (mode 0) and compressed (mode 1) ---------
 struct DenseArgs {

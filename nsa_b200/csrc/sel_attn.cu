@@ -1,4 +1,6 @@
-// Selected-block attention, query-major: forward (o_slc, lse_slc) and the dQ half of the backward.
+// Selected-block attention, query-major: forward (o_slc, lse_slc) and the dQ half of the backward.  General form for
+// any block size (16/32/64 keys) and any number of selected blocks; 64-key blocks with at most 32 selections per
+// query run the faster one-item-per-warp kernel of sel_block.cu instead.
 //
 // Reference behaviour: parallel_nsa_fwd_kernel (nsa/selection_attn.py:401-482) and the selected half
 // of parallel_nsa_bwd_kernel_dq (nsa/selection_attn.py:276-356).  A query (b, t, kv head) visits the
@@ -351,12 +353,14 @@ int launch(const SelArgs& a, cudaStream_t s) {
 }  // namespace
 
 int launch_sel_fwd(const SelArgs& a, int D, cudaStream_t s) {
+  if (sel_block_supported(a, D)) return launch_sel_block(a, D, false, s);
   if (D == 128) return launch<128, false>(a, s);
   if (D == 64) return launch<64, false>(a, s);
   set_error("head_dim %d not supported (64 or 128)", D);
   return -2;
 }
 int launch_sel_dq(const SelArgs& a, int D, cudaStream_t s) {
+  if (sel_block_supported(a, D)) return launch_sel_block(a, D, true, s);
   if (D == 128) return launch<128, true>(a, s);
   if (D == 64) return launch<64, true>(a, s);
   set_error("head_dim %d not supported (64 or 128)", D);
