@@ -24,7 +24,11 @@ namespace nsa {
 namespace {
 
 constexpr int D = 128;
-constexpr int kThreads = 320;              // warp 0 TMA, warp 1 MMA, warps 2-9 soft-max / epilogue
+constexpr int kProd = 3;                   // TMA producer warps (a warp's TMA instructions run one after another,
+                                           // ~900 cycles each whatever their size, so the boxes of a batch are
+                                           // spread over several warps and issued by one instruction per warp)
+constexpr int kMmaWarp = kProd;            // warps 0..kProd-1 TMA, warp kProd MMA, the next eight soft-max / epilogue
+constexpr int kThreads = (kProd + 1 + 8) * 32;
 constexpr int kSoftThreads = 256;          // two threads per row: key columns 0-31 and 32-63
 constexpr int kTokB = 8;                   // tokens per batch (x16 heads = 128 rows)
 constexpr uint32_t KV_PANEL = 64 * 128;    // [64 keys][64 ch]
@@ -71,7 +75,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                  tmem_slot = bar_base + 80;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(full0 + 8 * i, 1);
+      mbar_init(full0 + 8 * i, kProd);
       mbar_init(empty0 + 8 * i, 1);
     }
     mbar_init(kv_bar, 1);
@@ -82,7 +86,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(acc_full, 1);
     fence_mbar_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == kMmaWarp) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -97,11 +101,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     long long item = blockIdx.x;
     const int BH = a.B * a.Hk;
     if (MODE == 0) {
-      blk = (int)(item / BH);
-      const int bh = (int)(item % BH);
+      // (batch, kv head)-major: the CTAs resident at one time share one 16-head group's Q and dO rows (67 MB at
+      // T = 8192), which then stay in L2; block-major order made every gather a DRAM access
+      const int NB = (a.T + 63) / 64;
+      blk = (int)(item % NB);
+      const int bh = (int)(item / NB);
       b = bh / a.Hk;
       hk = bh % a.Hk;
-      const int NB = (a.T + 63) / 64;
       if (a.rev_ptr) {
         const int* rp = a.rev_ptr + (long long)bh * (NB + 1);
         st.ta_lo = rp[blk];
@@ -131,10 +137,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int nb_sub = nbA + nbB;             // batches per 16-head sub-group
   const int nb = skip ? 0 : nb_sub * G16;   // batches of this CTA
 
-  if (!skip && warp == 0) {
-    // ------------------------------- TMA producer ------------------------------------------------
-    // Lanes 0-7 fetch the 8 token ids of a batch one batch ahead; lane 0 waits for the stage and arms its barrier.
-    if (lane == 0) {
+  if (!skip && warp < kProd) {
+    // ------------------------------- TMA producers -----------------------------------------------
+    // A batch is 32 boxes of 2 KB: (token j, Q or dO, column panel).  Box x = 3 * lane + warp belongs to this lane;
+    // every producer warp issues its 10 or 11 boxes with a single instruction and arms the stage's barrier with
+    // their byte count.  Token ids are fetched one batch ahead.
+    if (warp == 0 && lane == 0) {
       mbar_expect_tx(kv_bar, 2 * KV_TILE);
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
@@ -142,11 +150,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         tma_load_4d(v_s + p * KV_PANEL, &tmV, kv_bar, p * 64, hk, key0, b);
       }
     }
+    const int x = kProd * lane + warp;          // this lane's box of every batch (none if >= 32)
+    const bool has = x < 4 * kTokB;
+    const int bj = x & 7, bwhich = (x >> 3) & 1, bp = x >> 4;
+    const int nmine = (4 * kTokB - warp + kProd - 1) / kProd;   // boxes this warp issues per batch
     auto batch_token = [&](int n) {
-      if (n >= nb) return 0;
+      if (n >= nb || !has) return 0;
       const int m = n % nb_sub;
       const int br = m < nbA ? 0 : 1;
-      return stream_token(st, br, (br == 0 ? m : m - nbA) * kTokB + (lane & 7));
+      return stream_token(st, br, (br == 0 ? m : m - nbA) * kTokB + bj);
     };
     int tk_next = batch_token(0);
     for (int n = 0; n < nb; ++n) {
@@ -162,21 +174,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       int good = 1;
       if (lane == 0) {
         good = mbar_wait(empty0 + 8 * stage, ph ^ 1, DEV_ERR_EMPTY_WAIT) ? 1 : 0;
-        if (good) mbar_expect_tx(fb, STAGE);
+        if (good) mbar_expect_tx(fb, nmine * 2048);
       }
       if (!__shfl_sync(0xffffffffu, good, 0)) break;
-      const uint32_t q_s = ring + stage * STAGE, do_s = q_s + Q_TILE;
-      // lanes 0-7 each issue the four boxes of their own token, so the issue latencies overlap
-      if (lane < kTokB) {
+      if (has) {
+        const uint32_t q_s = ring + stage * STAGE, do_s = q_s + Q_TILE;
         const int qrow = (int)(((long long)b * a.Tq + (tk - a.q0)) * a.Hq + hg * 16);
-#pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          tma_load_2d(q_s + p * Q_PANEL + lane * 2048, &tmQ, fb, p * 64, qrow);
-          tma_load_2d(do_s + p * Q_PANEL + lane * 2048, tmDO, fb, p * 64, qrow);
-        }
+        tma_load_2d((bwhich ? do_s : q_s) + bp * Q_PANEL + bj * 2048, bwhich ? tmDO : &tmQ, fb, bp * 64, qrow);
       }
     }
-  } else if (!skip && warp == 1) {
+  } else if (!skip && warp == kMmaWarp) {
     // ------------------------------- MMA issuer ----------------------------------------------------
     if (lane == 0 && nb > 0) {
       constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 64, 0, 0);   // both operands K-major
@@ -226,10 +233,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       umma_commit(acc_full);
     }
-  } else if (!skip && warp >= 2) {
+  } else if (!skip && warp > kMmaWarp) {
     // ------------------------------- soft-max warps: one (token, head) row per thread --------------
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;           // which 32 key columns this thread owns
+    const int half = (warp - kMmaWarp - 1) >> 2; // which 32 key columns this thread owns
     const int row = 32 * quad + lane;           // TMEM lane == tile row
     const int j = row >> 4, head = row & 15;
     const uint32_t lane_addr = (uint32_t)(32 * quad) << 16;
@@ -385,7 +392,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+  if (warp == kMmaWarp) tmem_dealloc(tmem, kTmemCols);
 }
 
 template <int MODE>

@@ -52,6 +52,23 @@ __device__ __forceinline__ void mma_a_bt_wide(float (&acc)[NK / 8][4], const uin
   }
 }
 
+// Hand a tile back after ldmatrix.  The loaded fragments are folded into `dep`, which is stored (volatile) to a scratch
+// word before the arrive: the store cannot be issued before the loads have returned, and neither the compiler nor
+// the assembler may drop it or move the arrive in front of it.  A plain arrive after the ldmatrix instructions is
+// not enough: nothing orders it behind loads whose results are not used yet.
+__device__ __forceinline__ void mbar_arrive_after(uint32_t bar, uint32_t scratch, uint32_t dep) {
+  asm volatile("st.volatile.shared::cta.u32 [%1], %2;\n\t{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar),
+               "r"(scratch), "r"(dep)
+               : "memory");
+}
+template <int N>
+__device__ __forceinline__ uint32_t fold_frags(const uint32_t (&f)[N][4]) {
+  uint32_t x = 0;
+#pragma unroll
+  for (int i = 0; i < N; ++i) x ^= f[i][0] ^ f[i][1] ^ f[i][2] ^ f[i][3];
+  return x;
+}
+
 struct Item {
   int b, tl, t, hkv;
   long long row;   // (b, tl, hkv) row of the index / counts tensors
@@ -108,6 +125,7 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
   auto qempty_bar = [&](int w) { return bar_base + 8u * (2 * nst + kWarps + w); };
   volatile int* abort_flag =
       reinterpret_cast<volatile int*>(sgen + (bar_base - sbase) + 8 * (2 * nst + 2 * kWarps));
+  const uint32_t dep_scratch = bar_base + 8u * (2 * nst + 2 * kWarps) + 16 + 4 * (warp % kWarps);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -212,9 +230,15 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
       bool ok = mbar_wait_abortable(qfull_bar(warp), qn & 1, DEV_ERR_FULL_WAIT, abort_flag);
       load_a_frags<D>(qf, qtile, qpanel_bytes, 0, lane);
       if constexpr (BWD) load_a_frags<D>(dof, qtile + qtile_bytes, qpanel_bytes, 0, lane);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(qempty_bar(warp));
       ++qn;
+      // The Q tile is handed back once its fragments are in registers (see mbar_arrive_after: a plain arrive here let
+      // the next item's TMA overwrite the tile before it had been read, one wrong item in roughly every fourth launch).
+      {
+        uint32_t dep = fold_frags(qf);
+        if constexpr (BWD) dep ^= fold_frags(dof);
+        dep = __reduce_or_sync(0xffffffffu, dep);   // every lane's fragments
+        if (lane == 0) mbar_arrive_after(qempty_bar(warp), dep_scratch, dep);
+      }
 
       while (my_mask) {
         const int bit = __ffs(my_mask) - 1;

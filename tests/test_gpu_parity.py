@@ -141,7 +141,8 @@ def _rand_indices(B, T, H, S, BS, gen, poison=True):
 
 
 @pytest.mark.parametrize("D,BS,S,Hq,Hkv,T,window", [(128, 64, 4, 32, 2, 384, 100), (64, 32, 5, 16, 1, 200, 0),
-                                                    (128, 16, 3, 16, 1, 130, 33)])
+                                                    (128, 16, 3, 16, 1, 130, 33), (64, 64, 6, 32, 2, 300, 0),
+                                                    (128, 64, 20, 16, 1, 450, 0)])
 def test_selection_and_window_fwd_bwd(nsa, D, BS, S, Hq, Hkv, T, window):
     gen = torch.Generator().manual_seed(1234 + D + BS)
     B = 2
