@@ -38,8 +38,9 @@ constexpr uint32_t Q_TILE = 2 * Q_PANEL;   // 32 KB
 constexpr uint32_t STAGE = 2 * Q_TILE;     // Q + dO
 constexpr uint32_t P_TILE = 128 * 128;     // [128 rows][64 keys]
 constexpr int kStages = 2;
-constexpr uint32_t kSmem = 2 * KV_TILE + kStages * STAGE + 2 * P_TILE + 256 + 1024;
-constexpr uint32_t kTmemCols = 256;        // S 0..63, dP 64..127, dV^T 128..191, dK^T 192..255
+constexpr uint32_t kSmem = 2 * KV_TILE + kStages * STAGE + 4 * P_TILE + 256 + 1024;
+constexpr uint32_t kTmemCols = 512;        // two S/dP buffers: S 0..63, dP 64..127 | 128..255; dV^T 256..319, dK^T 320..383
+constexpr uint32_t kColDV = 256, kColDK = 320;
 
 struct Stream {  // the token stream of one CTA: branch A (list or range) then branch B (window range)
   int nA, nB, ta_lo, tb_lo;
@@ -67,22 +68,26 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t k_s = sbase, v_s = sbase + KV_TILE;
   const uint32_t ring = sbase + 2 * KV_TILE;
-  const uint32_t p_s = ring + kStages * STAGE, ds_s = p_s + P_TILE;
-  const uint32_t bar_base = ds_s + P_TILE;
+  const uint32_t p_s0 = ring + kStages * STAGE;   // two [P | dS] tile pairs
+  const uint32_t bar_base = p_s0 + 4 * P_TILE;
   // barriers
+  // sdp_* and pds_* exist twice (index = batch & 1): S/dP of batch n+1 are computed while the soft-max warps still
+  // hold batch n, and P/dS of batch n+1 are written while dV/dK of batch n still read theirs
   const uint32_t full0 = bar_base, empty0 = bar_base + 16, kv_bar = bar_base + 32, sdp_full = bar_base + 40,
-                 sdp_free = bar_base + 48, pds_full = bar_base + 56, pds_free = bar_base + 64, acc_full = bar_base + 72,
-                 tmem_slot = bar_base + 80;
+                 sdp_free = bar_base + 56, pds_full = bar_base + 72, pds_free = bar_base + 88, acc_full = bar_base + 104,
+                 tmem_slot = bar_base + 112;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(full0 + 8 * i, kProd);
       mbar_init(empty0 + 8 * i, 1);
     }
     mbar_init(kv_bar, 1);
-    mbar_init(sdp_full, 1);
-    mbar_init(sdp_free, kSoftThreads);
-    mbar_init(pds_full, kSoftThreads);
-    mbar_init(pds_free, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(sdp_full + 8 * i, 1);
+      mbar_init(sdp_free + 8 * i, kSoftThreads);
+      mbar_init(pds_full + 8 * i, kSoftThreads);
+      mbar_init(pds_free + 8 * i, 1);
+    }
     mbar_init(acc_full, 1);
     fence_mbar_init();
   }
@@ -189,47 +194,80 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 64, 0, 0);   // both operands K-major
       constexpr uint32_t idesc_mn = umma_idesc_bf16(128, 64, 1, 1);   // both operands MN-major
       bool ok = mbar_wait(kv_bar, 0, DEV_ERR_FULL_WAIT);
-      auto issue_sdp = [&](int n) {
-        const uint32_t q_s = ring + (n % kStages) * STAGE, do_s = q_s + Q_TILE;
+      // descriptors of every operand tile are built once; an MMA then costs one 64-bit add per operand
+      const uint64_t dK = umma_smem_desc(k_s, 0, 1024), dV = umma_smem_desc(v_s, 0, 1024);
+      uint64_t dQk[kStages], dDOk[kStages], dQmn[kStages], dDOmn[kStages], dP[2], dDS[2];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t aoff = (ks >> 2) * Q_PANEL + (ks & 3) * 32, boff = (ks >> 2) * KV_PANEL + (ks & 3) * 32;
-          umma_ss(tmem + 0, umma_smem_desc(q_s + aoff, 0, 1024), umma_smem_desc(k_s + boff, 0, 1024), idesc_kk, ks ? 1u : 0u);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t aoff = (ks >> 2) * Q_PANEL + (ks & 3) * 32, boff = (ks >> 2) * KV_PANEL + (ks & 3) * 32;
-          umma_ss(tmem + 64, umma_smem_desc(do_s + aoff, 0, 1024), umma_smem_desc(v_s + boff, 0, 1024), idesc_kk, ks ? 1u : 0u);
-        }
-        umma_commit(sdp_full);
-      };
-      if (ok) ok = mbar_wait(full0, 0, DEV_ERR_FULL_WAIT);
-      if (ok) {
-        tc_fence_after();
-        issue_sdp(0);
+      for (int i = 0; i < kStages; ++i) {
+        const uint32_t q_s = ring + i * STAGE, do_s = q_s + Q_TILE;
+        dQk[i] = umma_smem_desc(q_s, 0, 1024);
+        dDOk[i] = umma_smem_desc(do_s, 0, 1024);
+        dQmn[i] = umma_smem_desc(q_s, Q_PANEL, 1024);
+        dDOmn[i] = umma_smem_desc(do_s, Q_PANEL, 1024);
       }
-      for (int n = 0; ok && n < nb; ++n) {
-        if (n + 1 < nb) {
-          ok = mbar_wait(full0 + 8 * ((n + 1) % kStages), ((n + 1) / kStages) & 1, DEV_ERR_FULL_WAIT) &&
-               mbar_wait(sdp_free, n & 1, DEV_ERR_FULL_WAIT);
-          if (!ok) break;
-          tc_fence_after();
-          issue_sdp(n + 1);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        dP[i] = umma_smem_desc(p_s0 + i * 2 * P_TILE, 0, 1024);
+        dDS[i] = umma_smem_desc(p_s0 + i * 2 * P_TILE + P_TILE, 0, 1024);
+      }
+      auto issue_sdp = [&](int n) {
+        const uint64_t aq = (n % kStages) ? dQk[1] : dQk[0], ado = (n % kStages) ? dDOk[1] : dDOk[0];
+        const uint32_t col = (n & 1) * 128;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t aoff = (ks >> 2) * Q_PANEL + (ks & 3) * 32, boff = (ks >> 2) * KV_PANEL + (ks & 3) * 32;
+          umma_ss(tmem + col, umma_desc_advance(aq, aoff), umma_desc_advance(dK, boff), idesc_kk, ks ? 1u : 0u);
         }
-        ok = mbar_wait(pds_full, n & 1, DEV_ERR_FULL_WAIT);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t q_s = ring + (n % kStages) * STAGE, do_s = q_s + Q_TILE;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t aoff = (ks >> 2) * Q_PANEL + (ks & 3) * 32, boff = (ks >> 2) * KV_PANEL + (ks & 3) * 32;
+          umma_ss(tmem + col + 64, umma_desc_advance(ado, aoff), umma_desc_advance(dV, boff), idesc_kk, ks ? 1u : 0u);
+        }
+        umma_commit(sdp_full + 8 * (n & 1));
+      };
+      auto issue_dkv = [&](int n) {
+        const uint64_t aq = (n % kStages) ? dQmn[1] : dQmn[0], ado = (n % kStages) ? dDOmn[1] : dDOmn[0];
+        const uint64_t bp = (n & 1) ? dP[1] : dP[0], bds = (n & 1) ? dDS[1] : dDS[0];
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)   // contraction over the 128 rows, 16 per step
-          umma_ss(tmem + 128, umma_smem_desc(do_s + ks * 2048, Q_PANEL, 1024), umma_smem_desc(p_s + ks * 2048, 0, 1024),
-                  idesc_mn, (n | ks) ? 1u : 0u);
+          umma_ss(tmem + kColDV, umma_desc_advance(ado, ks * 2048), umma_desc_advance(bp, ks * 2048), idesc_mn, (n | ks) ? 1u : 0u);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ss(tmem + 192, umma_smem_desc(q_s + ks * 2048, Q_PANEL, 1024), umma_smem_desc(ds_s + ks * 2048, 0, 1024),
-                  idesc_mn, (n | ks) ? 1u : 0u);
+          umma_ss(tmem + kColDK, umma_desc_advance(aq, ks * 2048), umma_desc_advance(bds, ks * 2048), idesc_mn, (n | ks) ? 1u : 0u);
         umma_commit(empty0 + 8 * (n % kStages));
-        umma_commit(pds_free);
+        umma_commit(pds_free + 8 * (n & 1));
+      };
+      // Event loop: S/dP of batch `ns` is issued as soon as its Q/dO stage has landed and its TMEM buffer is free,
+      // dV/dK of batch `nd` as soon as its P/dS tiles are written -- whichever becomes ready first.  Waiting for
+      // them in a fixed order left the tensor core idle for a whole TMA latency per batch: the stage of batch n+2
+      // is only freed by dV/dK of batch n, so a thread blocked on that stage could not issue dV/dK of batch n+1.
+      int ns = 0, nd = 0;
+      uint64_t t_idle = 0;
+      while (ok && nd < nb) {
+        bool progressed = false;
+        if (ns < nb && ns < nd + 2 && mbar_try(full0 + 8 * (ns % kStages), (ns / kStages) & 1) &&
+            (ns < 2 || mbar_try(sdp_free + 8 * (ns & 1), ((ns >> 1) - 1) & 1))) {
+          tc_fence_after();
+          issue_sdp(ns);
+          ++ns;
+          progressed = true;
+        }
+        if (nd < ns && mbar_try(pds_full + 8 * (nd & 1), (nd >> 1) & 1)) {
+          tc_fence_after();
+          issue_dkv(nd);
+          ++nd;
+          progressed = true;
+        }
+        if (progressed) {
+          t_idle = 0;
+        } else {   // bounded: ~2 s without any progress is reported as a pipeline failure
+          const uint64_t now = global_timer_ns();
+          if (t_idle == 0) t_idle = now;
+          else if (now - t_idle > 2000000000ull) {
+            atomicCAS(&g_dev_error, 0, (int)DEV_ERR_FULL_WAIT);
+            ok = false;
+          }
+        }
       }
       umma_commit(acc_full);
     }
@@ -293,19 +331,21 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool live = ri.live;
       const float lse2 = ri.lse2, del = ri.del, gv = ri.gv;
 
-      ok = mbar_wait(sdp_full, n & 1, DEV_ERR_FULL_WAIT);
+      const uint32_t buf = n & 1, use = n >> 1;
+      const uint32_t tcol = buf * 128;
+      ok = mbar_wait(sdp_full + 8 * buf, use & 1, DEV_ERR_FULL_WAIT);
       if (!ok) break;
       tc_fence_after();
       uint32_t pw[16], dw[16];   // 32 bf16 each
       {
         float sv[32], dpv[32];
-        tmem_ld16(tmem + lane_addr + half * 32, *reinterpret_cast<float(*)[16]>(&sv[0]));
-        tmem_ld16(tmem + lane_addr + half * 32 + 16, *reinterpret_cast<float(*)[16]>(&sv[16]));
-        tmem_ld16(tmem + lane_addr + 64 + half * 32, *reinterpret_cast<float(*)[16]>(&dpv[0]));
-        tmem_ld16(tmem + lane_addr + 64 + half * 32 + 16, *reinterpret_cast<float(*)[16]>(&dpv[16]));
+        tmem_ld16(tmem + lane_addr + tcol + half * 32, *reinterpret_cast<float(*)[16]>(&sv[0]));
+        tmem_ld16(tmem + lane_addr + tcol + half * 32 + 16, *reinterpret_cast<float(*)[16]>(&sv[16]));
+        tmem_ld16(tmem + lane_addr + tcol + 64 + half * 32, *reinterpret_cast<float(*)[16]>(&dpv[0]));
+        tmem_ld16(tmem + lane_addr + tcol + 64 + half * 32 + 16, *reinterpret_cast<float(*)[16]>(&dpv[16]));
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(sdp_free);   // S and dP are in registers: the next batch's S/dP may overwrite TMEM
+        mbar_arrive(sdp_free + 8 * buf);   // S and dP are in registers: batch n+2 may overwrite this TMEM buffer
         const int kfirst = key0 + half * 32, klast = kfirst + 31;
         bool all_valid;
         if (MODE == 0)
@@ -342,13 +382,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
-      if (n > 0) {
-        ok = mbar_wait(pds_free, (n - 1) & 1, DEV_ERR_EMPTY_WAIT);   // dV/dK of the previous batch have read P, dS
+      if (n >= 2) {
+        ok = mbar_wait(pds_free + 8 * buf, (use - 1) & 1, DEV_ERR_EMPTY_WAIT);   // dV/dK of batch n-2 have read this pair
         if (!ok) break;
       }
       // this thread's half of row `row` of the [128 x 64] bf16 tiles: 4 chunks of 16 bytes at swizzled positions
-      uint8_t* prow = sgen + (p_s - sbase) + row * 128;
-      uint8_t* drow = sgen + (ds_s - sbase) + row * 128;
+      uint8_t* prow = sgen + (p_s0 - sbase) + buf * 2 * P_TILE + row * 128;
+      uint8_t* drow = prow + P_TILE;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int pos = ((4 * half + c) ^ (row & 7)) * 16;
@@ -356,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         *reinterpret_cast<uint4*>(drow + pos) = make_uint4(dw[4 * c], dw[4 * c + 1], dw[4 * c + 2], dw[4 * c + 3]);
       }
       fence_proxy_async();
-      mbar_arrive(pds_full);
+      mbar_arrive(pds_full + 8 * buf);
     }
     // ---- epilogue: dV^T / dK^T [d lanes x 64 key columns] -> global ---------------------------------------
     if (ok && nb > 0) ok = mbar_wait(acc_full, 0, DEV_ERR_FULL_WAIT);
@@ -368,7 +408,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int c = 0; c < 4; ++c) {
         float vals[16];
         if (nb > 0) {
-          tmem_ld16(tmem + lane_addr + 128 + which * 64 + c * 16, vals);
+          tmem_ld16(tmem + lane_addr + kColDV + which * 64 + c * 16, vals);
           tmem_ld_wait();
         } else {
 #pragma unroll

@@ -19,6 +19,11 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo,
   return d;
 }
 
+// The descriptor of the same layout `bytes` further on in shared memory.  The start-address field holds address >> 4
+// in 14 bits; shared memory ends below 256 KB, so the sum never carries out of the field.  Building a descriptor
+// once and stepping it with one add keeps the single MMA-issuing thread off the critical path.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
+
 // Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, M x N tile, operand majors (0 = K-major, 1 = MN-major).
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
