@@ -189,7 +189,11 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
     dwk = torch.empty(c["block"] * D, D, dtype=torch.float32, device=q4.device)
     dbk = torch.empty(D, dtype=torch.float32, device=q4.device)
     ws3 = torch.empty(L.nsa_compress_bwd_workspace_bytes(B, Hkv, D, c["block"]), dtype=torch.uint8, device=q4.device)
-    g1 = torch.full((B, T, Hq), 0.5, dtype=torch.bfloat16, device=q4.device)
+    g1, g2, g3, dg1, dg2, dg3 = (torch.full((B, T, Hq), 0.5, dtype=torch.bfloat16, device=q4.device) for _ in range(6))
+    delta2, delta3 = torch.empty_like(delta), torch.empty_like(delta)
+    wg, bg = mod.gating.weight.detach(), mod.gating.bias.detach()
+    dwg, dbg = torch.empty_like(wg), torch.empty_like(bg)
+    ws4 = torch.empty(L.nsa_gate_bwd_workspace_bytes(B * T * Hq, D), dtype=torch.uint8, device=q4.device)
 
     calls = {
         "compress_fwd(one of k,v)": lambda: L.nsa_compress_fwd_uniform(P(k3), P(wk), P(bk), P(ck), B, T, Hkv, D, c["block"],
@@ -204,7 +208,9 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
                                              None, None, None, None, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"],
                                              c["window"], scale, S()),
         "combine": lambda: L.nsa_combine(P(o_slc), P(g1), P(o_swa), P(g1), P(o_cmp), P(g1), P(dq), B * T * Hq, D, S()),
-        "rowdot(delta)": lambda: L.nsa_rowdot(P(o_slc), P(do4), None, P(delta), None, B * T * Hq, D, S()),
+        "gate_fwd": lambda: L.nsa_gate_fwd(P(q4), P(wg), P(bg), P(g1), P(g2), P(g3), B * T * Hq, D, S()),
+        "rowdot3(delta,dgate)": lambda: L.nsa_rowdot3(P(o_slc), P(o_swa), P(o_cmp), P(do4), P(g1), P(g2), P(g3), P(delta),
+                                                      P(delta2), P(delta3), P(dg1), P(dg2), P(dg3), B * T * Hq, D, S()),
         "sel_dq": lambda: L.nsa_sel_swa_bwd(P(q4), P(k4), P(v4), P(idx), 0, None, P(do4), P(lse_slc), P(delta), None, None,
                                             None, None, None, P(dq), 0, None, None, None, 0, B, T, Hq, Hkv, D, c["n_sel"],
                                             c["sel_block"], 0, scale, S()),
@@ -220,6 +226,8 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
         "cmp_dkv(+reduce)": lambda: L.nsa_cmp_attn_bwd(P(q4), P(ck), P(cv), P(lse_cmp), P(do4), P(delta), None, None, 0,
                                                        P(dck), P(dcv), P(ws2), ws2.numel(), B, T, Tc, Hq, Hkv, D,
                                                        c["block"], c["stride"], 1, scale, S()),
+        "gate_bwd": lambda: L.nsa_gate_bwd(P(q4), P(dg1), P(dg2), P(dg3), P(wg), P(dq), P(dwg), P(dbg), P(ws4), ws4.numel(),
+                                           B * T * Hq, D, S()),
         "compress_bwd(one of k,v)": lambda: L.nsa_compress_bwd(P(k3), P(wk), P(dck), P(dk), P(dwk), P(dbk), P(ws3),
                                                                 ws3.numel(), P(cin), P(cout), B, Hkv, D, c["block"],
                                                                 c["stride"], T, B * Tc, S()),

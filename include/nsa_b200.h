@@ -155,6 +155,22 @@ int nsa_decode_fwd(const void* q, const void* k, const void* v, const void* ck, 
  * (nsa/triton_attention.py:184-199) and the gate gradients of the addcmul at nsa/nsa.py:133. */
 int nsa_rowdot(const void* o, const void* dout, const void* gate, float* delta, void* dgate, long long rows, int D,
                void* stream);
+/* The gate projection of the module: g_x[r] = q[r,:] . w[x,:] + bias[x] for x = 0,1,2 = selected, window, compressed
+ * (w [3,D] bf16, bias [3] bf16 or NULL; no activation), each gate written to its own contiguous [rows] bf16 tensor.
+ * Replaces self.gating = nn.Linear(head_dim, 3) applied at nsa/nsa.py:117. */
+int nsa_gate_fwd(const void* q, const void* w, const void* bias, void* g_slc, void* g_swa, void* g_cmp, long long rows,
+                 int D, void* stream);
+/* nsa_rowdot for the three branches in one pass over dout (a NULL o_x drops that branch): delta_x = g_x * rowsum(o_x *
+ * dout), dg_x = rowsum(o_x * dout).  Same reference lines as nsa_rowdot. */
+int nsa_rowdot3(const void* o_slc, const void* o_swa, const void* o_cmp, const void* dout, const void* g_slc,
+                const void* g_swa, const void* g_cmp, float* delta_slc, float* delta_swa, float* delta_cmp, void* dg_slc,
+                void* dg_swa, void* dg_cmp, long long rows, int D, void* stream);
+/* Backward of the gate projection (the autograd of nn.Linear at nsa/nsa.py:117): dq[r,:] += sum_x dg_x[r] * w[x,:] in
+ * place, dw[x,:] = sum_r dg_x[r] * q[r,:], dbias[x] = sum_r dg_x[r] (NULL to skip).  Deterministic: fixed-order
+ * partial sums in `workspace` (nsa_gate_bwd_workspace_bytes), no atomics. */
+long long nsa_gate_bwd_workspace_bytes(long long rows, int D);
+int nsa_gate_bwd(const void* q, const void* dg_slc, const void* dg_swa, const void* dg_cmp, const void* w, void* dq,
+                 void* dw, void* dbias, void* workspace, long long workspace_bytes, long long rows, int D, void* stream);
 /* o = g0*a0 + g1*a1 + g2*a2 (NULL tensor: term dropped; NULL gate: 1).  nsa/nsa.py:133. */
 int nsa_combine(const void* a0, const void* g0, const void* a1, const void* g1, const void* a2, const void* g2,
                 void* o, long long rows, int D, void* stream);

@@ -40,6 +40,10 @@ SIGNATURES = {
     "nsa_decode_fwd": (I, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P]),
     "nsa_rowdot": (I, [P, P, P, P, P, L, I, P]),
     "nsa_combine": (I, [P, P, P, P, P, P, P, L, I, P]),
+    "nsa_gate_fwd": (I, [P, P, P, P, P, P, L, I, P]),
+    "nsa_rowdot3": (I, [P] * 13 + [L, I, P]),
+    "nsa_gate_bwd_workspace_bytes": (L, [L, I]),
+    "nsa_gate_bwd": (I, [P] * 9 + [L, L, I, P]),
 }
 
 _lib = None

@@ -82,13 +82,12 @@ def context_parallel_forward(module, q, k, v, group=None, zigzag=True, causal=Tr
     scale = module.softmax_scale
     if scale is None or scale is True:
         scale = 1.0 if scale is True else D ** -0.5
-    gates = module.gating(q)
     outs = []
     for i, cid in enumerate(layout[rank]):
         sl = slice(i * cl, (i + 1) * cl)
-        g_slc, g_swa, g_cmp = (g.contiguous() for g in gates[:, sl].unbind(-1))
         cfg = (module.compression_stride, module.compression_block, bool(causal), float(scale), module.pool_kernel_size,
                module.pool_stride, module.pool_padding, module.selected_block_count, module.selection_block_size,
                module.sliding_window, cid * cl)
-        outs.append(_NSACore.apply(q[:, sl].contiguous(), k_full, v_full, ck, cv, g_slc, g_swa, g_cmp, cfg))
+        outs.append(_NSACore.apply(q[:, sl].contiguous(), k_full, v_full, ck, cv, module.gating.weight, module.gating.bias,
+                                   cfg))
     return torch.cat(outs, dim=1)

@@ -451,6 +451,34 @@ int nsa_rowdot(const void* o, const void* dout, const void* gate, float* delta, 
                        (cudaStream_t)stream);
 }
 
+int nsa_gate_fwd(const void* q, const void* w, const void* bias, void* g_slc, void* g_swa, void* g_cmp, long long rows,
+                 int D, void* stream) {
+  if (!q || !w || !g_slc || !g_swa || !g_cmp) return fail(-1, "nsa_gate_fwd: null pointer");
+  return launch_gate_fwd((const bf16*)q, (const bf16*)w, (const bf16*)bias, (bf16*)g_slc, (bf16*)g_swa, (bf16*)g_cmp, rows,
+                         D, (cudaStream_t)stream);
+}
+
+int nsa_rowdot3(const void* o_slc, const void* o_swa, const void* o_cmp, const void* dout, const void* g_slc,
+                const void* g_swa, const void* g_cmp, float* delta_slc, float* delta_swa, float* delta_cmp, void* dg_slc,
+                void* dg_swa, void* dg_cmp, long long rows, int D, void* stream) {
+  if (!dout) return fail(-1, "nsa_rowdot3: null upstream gradient");
+  const bf16* o[3] = {(const bf16*)o_slc, (const bf16*)o_swa, (const bf16*)o_cmp};
+  const bf16* g[3] = {(const bf16*)g_slc, (const bf16*)g_swa, (const bf16*)g_cmp};
+  float* dl[3] = {delta_slc, delta_swa, delta_cmp};
+  bf16* dg[3] = {(bf16*)dg_slc, (bf16*)dg_swa, (bf16*)dg_cmp};
+  return launch_rowdot3(o, (const bf16*)dout, g, dl, dg, rows, D, (cudaStream_t)stream);
+}
+
+long long nsa_gate_bwd_workspace_bytes(long long rows, int D) { return gate_bwd_workspace_bytes(rows, D); }
+
+int nsa_gate_bwd(const void* q, const void* dg_slc, const void* dg_swa, const void* dg_cmp, const void* w, void* dq,
+                 void* dw, void* dbias, void* workspace, long long workspace_bytes, long long rows, int D, void* stream) {
+  if (!q || !dg_slc || !dg_swa || !dg_cmp || !w || !dq || !dw || !workspace) return fail(-1, "nsa_gate_bwd: null pointer");
+  if (workspace_bytes < gate_bwd_workspace_bytes(rows, D)) return fail(-3, "nsa_gate_bwd: workspace too small");
+  return launch_gate_bwd((const bf16*)q, (const bf16*)dg_slc, (const bf16*)dg_swa, (const bf16*)dg_cmp, (const bf16*)w,
+                         (bf16*)dq, (bf16*)dw, (bf16*)dbias, (float*)workspace, rows, D, (cudaStream_t)stream);
+}
+
 int nsa_combine(const void* a0, const void* g0, const void* a1, const void* g1, const void* a2, const void* g2, void* o,
                 long long rows, int D, void* stream) {
   if (!o) return fail(-1, "nsa_combine: null output");

@@ -1,0 +1,320 @@
+// The gate projection and the row-wise pre-pass of the backward, as HBM-bound streaming kernels.
+//
+// Reference behaviour: NSAAttention.gating = nn.Linear(head_dim, 3) applied to q, no activation (nsa/nsa.py:59,117);
+// its autograd (dq += dgates . W, dW = dgates^T . q, db = sum dgates); delta = rowsum(o * dO) of the three branches
+// (nsa/selection_attn.py:572-590, nsa/triton_attention.py:184-199) and the gradient of each gate, rowsum(o_x * dO).
+//
+// Every kernel gives half a warp to a (token, head) row: a lane owns 16 bytes (8 channels) of a 128-channel row, or
+// a quarter warp does for 64 channels, so a warp keeps several 16-byte loads per tensor in flight.  q, o and dO are
+// read exactly once per kernel.  dW and db are reduced without atomics: per-lane partial sums over the rows a lane
+// visits, a fixed-order reduction in the block, one partial per block in a caller-provided workspace, and a final
+// single-block reduction in block order, so results do not depend on scheduling.
+#include "kernels.h"
+#include "tmap.h"
+
+namespace nsa {
+
+namespace {
+
+constexpr int kGateThreads = 256;
+
+__device__ __forceinline__ uint4 ldraw(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void cvt8(const uint4& v, float (&x)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(h[k]);
+    x[2 * k] = f.x;
+    x[2 * k + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&x)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(h[k]);
+    x[2 * k] = f.x;
+    x[2 * k + 1] = f.y;
+  }
+}
+
+// sum over the LPR lanes that share a row (LPR = 16 or 8, a power of two, aligned groups)
+template <int LPR>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int off = LPR / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+// gates[row][g] = q[row] . W[g] + b[g], written to three contiguous [rows] tensors
+template <int D>
+__global__ void __launch_bounds__(kGateThreads) gate_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w,
+                                                               const bf16* __restrict__ bias, bf16* __restrict__ g0,
+                                                               bf16* __restrict__ g1, bf16* __restrict__ g2, long long rows) {
+  constexpr int LPR = D / 8;                 // lanes per row
+  constexpr int RPW = 32 / LPR;              // rows per warp and pass
+  const int lane = threadIdx.x & 31, sub = lane % LPR, rw = lane / LPR;
+  float wv[3][8], bv[3];
+#pragma unroll
+  for (int g = 0; g < 3; ++g) {
+    load8(w + g * D + sub * 8, wv[g]);
+    bv[g] = bias ? __bfloat162float(bias[g]) : 0.f;
+  }
+  const long long warp0 = (long long)blockIdx.x * (kGateThreads / 32) + (threadIdx.x >> 5);
+  const long long nwarp = (long long)gridDim.x * (kGateThreads / 32);
+  constexpr int U = 8;   // rows in flight per lane (raw 16-byte loads, converted when used)
+  for (long long r0 = warp0 * RPW * U; r0 < rows; r0 += nwarp * RPW * U) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + rw;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (row < rows) raw[u] = ldraw(q + row * D + sub * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + rw;
+      float xu[8];
+      cvt8(raw[u], xu);
+      float acc[3];
+#pragma unroll
+      for (int g = 0; g < 3; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += xu[k] * wv[g][k];
+        acc[g] = group_sum<LPR>(s) + bv[g];
+      }
+      if (row < rows && sub == 0) {
+        g0[row] = __float2bfloat16(acc[0]);
+        g1[row] = __float2bfloat16(acc[1]);
+        g2[row] = __float2bfloat16(acc[2]);
+      }
+    }
+  }
+}
+
+// For up to three branches x: delta_x[row] = gate_x[row] * rowsum(o_x * dO), dgate_x[row] = rowsum(o_x * dO).
+struct Rowdot3Args {
+  const bf16* o[3];
+  const bf16* gate[3];
+  float* delta[3];
+  bf16* dgate[3];
+  const bf16* dout;
+  long long rows;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kGateThreads) rowdot3_kernel(const Rowdot3Args a) {
+  constexpr int LPR = D / 8, RPW = 32 / LPR;
+  const int lane = threadIdx.x & 31, sub = lane % LPR, rw = lane / LPR;
+  const long long warp0 = (long long)blockIdx.x * (kGateThreads / 32) + (threadIdx.x >> 5);
+  const long long nwarp = (long long)gridDim.x * (kGateThreads / 32);
+  constexpr int U = 4;   // rows in flight per lane (x 4 tensors, raw 16-byte loads)
+  for (long long r0 = warp0 * RPW * U; r0 < a.rows; r0 += nwarp * RPW * U) {
+    uint4 draw[U], vraw[U][3];
+    float gv[U][3];   // the gates are fetched with the rows, not after the reductions that need them
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + rw;
+      const bool live = row < a.rows;
+      draw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (live) draw[u] = ldraw(a.dout + row * D + sub * 8);
+#pragma unroll
+      for (int x = 0; x < 3; ++x) {
+        vraw[u][x] = make_uint4(0u, 0u, 0u, 0u);
+        gv[u][x] = 1.f;
+        if (live && a.o[x]) vraw[u][x] = ldraw(a.o[x] + row * D + sub * 8);
+        if (live && sub == 0 && a.o[x] && a.gate[x]) gv[u][x] = __bfloat162float(a.gate[x][row]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + rw;
+      const bool live = row < a.rows;
+      float du[8];
+      cvt8(draw[u], du);
+#pragma unroll
+      for (int x = 0; x < 3; ++x) {
+        if (!a.o[x]) continue;   // uniform
+        float vu[8];
+        cvt8(vraw[u][x], vu);
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += vu[k] * du[k];
+        s = group_sum<LPR>(s);
+        if (live && sub == 0) {
+          if (a.delta[x]) a.delta[x][row] = s * gv[u][x];
+          if (a.dgate[x]) a.dgate[x][row] = __float2bfloat16(s);
+        }
+      }
+    }
+  }
+}
+
+// dq[row] += sum_g dg_g[row] * W[g];  per-block partials of dW[g] = sum_rows dg_g[row] * q[row] and db[g] = sum_rows dg_g
+template <int D>
+__global__ void __launch_bounds__(kGateThreads, 2) gate_bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ dg0,
+                                                               const bf16* __restrict__ dg1, const bf16* __restrict__ dg2,
+                                                               const bf16* __restrict__ w, bf16* __restrict__ dq,
+                                                               float* __restrict__ part, long long rows) {
+  constexpr int LPR = D / 8, RPW = 32 / LPR;
+  constexpr int NW = kGateThreads / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane % LPR, rw = lane / LPR;
+  float wv[3][8];
+#pragma unroll
+  for (int g = 0; g < 3; ++g) load8(w + g * D + sub * 8, wv[g]);
+  float dwacc[3][8], dbacc[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+  for (int g = 0; g < 3; ++g)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) dwacc[g][k] = 0.f;
+  const long long warp0 = (long long)blockIdx.x * NW + warp;
+  const long long nwarp = (long long)gridDim.x * NW;
+  constexpr int U = 4;   // rows in flight per lane: all loads of a pass are issued before the first store
+  for (long long r0 = warp0 * RPW * U; r0 < rows; r0 += nwarp * RPW * U) {
+    uint4 xraw[U], yraw[U];
+    float g[U][3];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + rw;
+      xraw[u] = yraw[u] = make_uint4(0u, 0u, 0u, 0u);
+      g[u][0] = g[u][1] = g[u][2] = 0.f;
+      if (row < rows) {
+        xraw[u] = ldraw(q + row * D + sub * 8);
+        yraw[u] = ldraw(dq + row * D + sub * 8);
+        g[u][0] = __bfloat162float(dg0[row]);
+        g[u][1] = __bfloat162float(dg1[row]);
+        g[u][2] = __bfloat162float(dg2[row]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + rw;
+      float xu[8], yu[8];
+      cvt8(xraw[u], xu);
+      cvt8(yraw[u], yu);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        yu[k] += g[u][0] * wv[0][k] + g[u][1] * wv[1][k] + g[u][2] * wv[2][k];
+#pragma unroll
+        for (int gg = 0; gg < 3; ++gg) dwacc[gg][k] += g[u][gg] * xu[k];
+      }
+      if (sub == 0) {
+#pragma unroll
+        for (int gg = 0; gg < 3; ++gg) dbacc[gg] += g[u][gg];
+      }
+      if (row < rows) {
+        uint4 out;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(yu[2 * k], yu[2 * k + 1]);
+        *reinterpret_cast<uint4*>(dq + row * D + sub * 8) = out;
+      }
+    }
+  }
+  // block reduction in a fixed order: slot (warp, row group) of every channel, then warps and groups in sequence
+  __shared__ float red[NW * RPW][3 * D + 4];
+  float* mine = red[warp * RPW + rw];
+#pragma unroll
+  for (int g = 0; g < 3; ++g)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) mine[g * D + sub * 8 + k] = dwacc[g][k];
+  if (sub == 0) {
+#pragma unroll
+    for (int g = 0; g < 3; ++g) mine[3 * D + g] = dbacc[g];
+  }
+  __syncthreads();
+  float* dst = part + (long long)blockIdx.x * (3 * D + 4);
+  for (int i = threadIdx.x; i < 3 * D + 3; i += kGateThreads) {
+    float s = 0.f;
+#pragma unroll 4
+    for (int j = 0; j < NW * RPW; ++j) s += red[j][i];
+    dst[i] = s;
+  }
+}
+
+// dW[g][c] and db[g] = sum over the block partials, in block order (one thread per output)
+__global__ void gate_reduce_kernel(const float* __restrict__ part, int nblk, int D, bf16* __restrict__ dw,
+                                   bf16* __restrict__ db) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 3 * D + 3) return;
+  float s = 0.f;
+  for (int b = 0; b < nblk; ++b) s += part[(long long)b * (3 * D + 4) + i];
+  if (i < 3 * D)
+    dw[i] = __float2bfloat16(s);
+  else if (db)
+    db[i - 3 * D] = __float2bfloat16(s);
+}
+
+int stream_grid(long long rows, int rows_per_block) {
+  const long long want = (rows + 4 * rows_per_block - 1) / (4 * rows_per_block);
+  const long long cap = (long long)num_sms() * 8;
+  return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+}  // namespace
+
+int launch_gate_fwd(const bf16* q, const bf16* w, const bf16* bias, bf16* g0, bf16* g1, bf16* g2, long long rows, int D,
+                    cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (D == 128)
+    gate_fwd_kernel<128><<<stream_grid(rows, 16), kGateThreads, 0, s>>>(q, w, bias, g0, g1, g2, rows);
+  else if (D == 64)
+    gate_fwd_kernel<64><<<stream_grid(rows, 32), kGateThreads, 0, s>>>(q, w, bias, g0, g1, g2, rows);
+  else {
+    set_error("head_dim %d not supported (64 or 128)", D);
+    return -2;
+  }
+  note_launches(1);
+  return (int)cudaGetLastError();
+}
+
+int launch_rowdot3(const bf16* const o[3], const bf16* dout, const bf16* const gate[3], float* const delta[3],
+                   bf16* const dgate[3], long long rows, int D, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  Rowdot3Args a;
+  for (int x = 0; x < 3; ++x) {
+    a.o[x] = o[x];
+    a.gate[x] = gate[x];
+    a.delta[x] = delta[x];
+    a.dgate[x] = dgate[x];
+  }
+  a.dout = dout;
+  a.rows = rows;
+  if (D == 128)
+    rowdot3_kernel<128><<<stream_grid(rows, 16), kGateThreads, 0, s>>>(a);
+  else if (D == 64)
+    rowdot3_kernel<64><<<stream_grid(rows, 32), kGateThreads, 0, s>>>(a);
+  else {
+    set_error("head_dim %d not supported (64 or 128)", D);
+    return -2;
+  }
+  note_launches(1);
+  return (int)cudaGetLastError();
+}
+
+// workspace: one partial of 3*D+4 floats per block
+long long gate_bwd_workspace_bytes(long long rows, int D) {
+  const int grid = stream_grid(rows, D == 128 ? 16 : 32);
+  return (long long)grid * (3 * D + 4) * 4;
+}
+
+int launch_gate_bwd(const bf16* q, const bf16* dg0, const bf16* dg1, const bf16* dg2, const bf16* w, bf16* dq, bf16* dw,
+                    bf16* db, float* workspace, long long rows, int D, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  const int grid = stream_grid(rows, D == 128 ? 16 : 32);
+  if (D == 128)
+    gate_bwd_kernel<128><<<grid, kGateThreads, 0, s>>>(q, dg0, dg1, dg2, w, dq, workspace, rows);
+  else if (D == 64)
+    gate_bwd_kernel<64><<<grid, kGateThreads, 0, s>>>(q, dg0, dg1, dg2, w, dq, workspace, rows);
+  else {
+    set_error("head_dim %d not supported (64 or 128)", D);
+    return -2;
+  }
+  gate_reduce_kernel<<<(3 * D + 3 + 127) / 128, 128, 0, s>>>(workspace, grid, D, dw, db);
+  note_launches(2);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace nsa

@@ -134,6 +134,14 @@ int compress_tc_status(int* out);
 int launch_rowdot(const bf16* o, const bf16* dout, const bf16* gate, float* delta, bf16* dgate, long long rows, int D,
                   cudaStream_t s);
 // o = g0*a0 + g1*a1 + g2*a2  (null pairs skipped); gates [rows], tensors [rows,D]
+// gate projection, fused row pre-pass of the backward, gate backward (gate.cu)
+int launch_gate_fwd(const bf16* q, const bf16* w, const bf16* bias, bf16* g0, bf16* g1, bf16* g2, long long rows, int D,
+                    cudaStream_t s);
+int launch_rowdot3(const bf16* const o[3], const bf16* dout, const bf16* const gate[3], float* const delta[3],
+                   bf16* const dgate[3], long long rows, int D, cudaStream_t s);
+long long gate_bwd_workspace_bytes(long long rows, int D);
+int launch_gate_bwd(const bf16* q, const bf16* dg0, const bf16* dg1, const bf16* dg2, const bf16* w, bf16* dq, bf16* dw,
+                    bf16* db, float* workspace, long long rows, int D, cudaStream_t s);
 int launch_combine(const bf16* a0, const bf16* g0, const bf16* a1, const bf16* g1, const bf16* a2, const bf16* g2,
                    bf16* o, long long rows, int D, cudaStream_t s);
 // reverse index of the selection: for every (b,h,block) the ascending list of tokens selecting it.

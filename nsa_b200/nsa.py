@@ -14,16 +14,21 @@ class _NSACore(torch.autograd.Function):
     to the kernels (no g*dO tensors are materialised, dQ is accumulated inside the kernels instead of by autograd)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, ck, cv, g_slc, g_swa, g_cmp, cfg):
-        """q, gates: [B,Tq,Hq,(D)] = the queries at sequence positions q0 .. q0+Tq-1; k, v: [B,T,Hkv,D] and ck, cv:
-        [B,Tc,Hkv,D] cover the whole sequence.  cfg[-1] = q0 (0 and Tq == T for an unsharded call)."""
+    def forward(ctx, q, k, v, ck, cv, w_gate, b_gate, cfg):
+        """q: [B,Tq,Hq,D] = the queries at sequence positions q0 .. q0+Tq-1; k, v: [B,T,Hkv,D] and ck, cv:
+        [B,Tc,Hkv,D] cover the whole sequence; w_gate [3,D], b_gate [3]: the gate projection (rows: selected,
+        window, compressed; nsa/nsa.py:59,117).  cfg[-1] = q0 (0 and Tq == T for an unsharded call)."""
         (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window, q0) = cfg
         q, k, v, ck, cv = (_lib.require(t, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (ck, "ck"), (cv, "cv")))
-        g_slc, g_swa, g_cmp = (_lib.require(t, "gate") for t in (g_slc, g_swa, g_cmp))
+        w_gate = _lib.require(w_gate, "gating.weight")
+        b_gate = _lib.require(b_gate, "gating.bias") if b_gate is not None else None
         B, Tq, Hq, D = q.shape
         T, Hkv, Tc = k.shape[1], k.shape[2], ck.shape[1]
         L, P, S = _lib.lib(), _lib.ptr, _lib.stream
         dev = q.device
+        g_slc, g_swa, g_cmp = (torch.empty(B, Tq, Hq, dtype=q.dtype, device=dev) for _ in range(3))
+        _lib.check(L.nsa_gate_fwd(P(q), P(w_gate), P(b_gate), P(g_slc), P(g_swa), P(g_cmp), B * Tq * Hq, D, S()),
+                   "nsa_gate_fwd")
         n_pool = L.nsa_pool_out_len(Tc, pool_k, pool_s, pool_p)
         if n_sel > n_pool:
             raise RuntimeError("selected index k out of range: %d blocks requested, %d exist" % (n_sel, n_pool))
@@ -38,13 +43,16 @@ class _NSACore(torch.autograd.Function):
         _lib.check(L.nsa_sel_swa_fwd_sharded(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(lse_slc), P(o_swa),
                                              P(lse_swa), P(g_slc), P(g_swa), P(o_cmp), P(g_cmp), P(o), B, T, Hq, Hkv, D,
                                              n_sel, sel_block, window, scale, Tq, q0, S()), "nsa_sel_swa_fwd")
-        ctx.save_for_backward(q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx)
+        ctx.save_for_backward(q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx,
+                              w_gate)
         ctx.cfg = cfg
+        ctx.has_bias = b_gate is not None
         return o
 
     @staticmethod
     def backward(ctx, do):
-        (q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx) = ctx.saved_tensors
+        (q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx,
+         w_gate) = ctx.saved_tensors
         (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window, q0) = ctx.cfg
         do = _lib.require(do, "do")
         B, Tq, Hq, D = q.shape
@@ -53,15 +61,14 @@ class _NSACore(torch.autograd.Function):
         dev = q.device
         rows = B * Tq * Hq
 
-        def delta_and_dgate(o_x, g_x):
-            delta = torch.empty(B, Tq, Hq, dtype=torch.float32, device=dev)
-            dg = torch.empty_like(g_x)
-            _lib.check(L.nsa_rowdot(P(o_x), P(do), P(g_x), P(delta), P(dg), rows, D, S()), "nsa_rowdot")
-            return delta, dg
-
-        delta_slc, dg_slc = delta_and_dgate(o_slc, g_slc)
-        delta_cmp, dg_cmp = delta_and_dgate(o_cmp, g_cmp)
-        delta_swa, dg_swa = delta_and_dgate(o_swa, g_swa) if window > 0 else (None, None)
+        # one pass over dO: delta = g * rowsum(o * dO) and the gate gradients rowsum(o * dO) of all three branches
+        delta_slc, delta_cmp = (torch.empty(B, Tq, Hq, dtype=torch.float32, device=dev) for _ in range(2))
+        delta_swa = torch.empty_like(delta_slc) if window > 0 else None
+        dg_slc, dg_swa, dg_cmp = (torch.empty_like(g_slc) for _ in range(3))
+        if window <= 0:
+            dg_swa.zero_()
+        _lib.check(L.nsa_rowdot3(P(o_slc), P(o_swa), P(o_cmp), P(do), P(g_slc), P(g_swa), P(g_cmp), P(delta_slc),
+                                 P(delta_swa), P(delta_cmp), P(dg_slc), P(dg_swa), P(dg_cmp), rows, D, S()), "nsa_rowdot3")
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         ws_bytes = L.nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, n_sel, sel_block)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
@@ -75,7 +82,14 @@ class _NSACore(torch.autograd.Function):
         _lib.check(L.nsa_cmp_attn_bwd_sharded(P(q), P(ck), P(cv), P(lse_cmp), P(do), P(delta_cmp), P(g_cmp), P(dq), 1,
                                               P(dck), P(dcv), P(ws), ws_bytes, B, T, Tc, Hq, Hkv, D, block, stride,
                                               1 if causal else 0, scale, Tq, q0, S()), "nsa_cmp_attn_bwd")
-        return dq, dk, dv, dck, dcv, dg_slc, dg_swa, dg_cmp, None
+        # gate projection backward: dq += dg . W in place (dq is complete here), dW and db by fixed-order reduction
+        dw = torch.empty_like(w_gate)
+        db = torch.empty(3, dtype=w_gate.dtype, device=dev) if ctx.has_bias else None
+        ws_bytes = L.nsa_gate_bwd_workspace_bytes(rows, D)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        _lib.check(L.nsa_gate_bwd(P(q), P(dg_slc), P(dg_swa), P(dg_cmp), P(w_gate), P(dq), P(dw), P(db), P(ws), ws_bytes,
+                                  rows, D, S()), "nsa_gate_bwd")
+        return dq, dk, dv, dck, dcv, dw, db, None
 
 
 class NSAAttention(nn.Module):
@@ -146,12 +160,11 @@ class NSAAttention(nn.Module):
 
         # compressed keys/values stay in the compact [B,Tc,Hkv,D] form (no repeat to Hq heads)
         ck, cv, _ = self.compressor(k, v, cu_seqlens_k, None)
-        gating_score = self.gating(q4)                         # [B,T,Hq,3], no activation
-        g_slc, g_swa, g_cmp = (g.contiguous() for g in gating_score.unbind(-1))
         k4 = k.reshape(bs, -1, num_kv_head, head_qk_dim)
         v4 = v.reshape(bs, -1, num_kv_head, head_v_dim)
         cfg = (self.compression_stride, self.compression_block, bool(causal), float(scale), self.pool_kernel_size,
                self.pool_stride, self.pool_padding, self.selected_block_count, self.selection_block_size,
                self.sliding_window, 0)
-        o = _NSACore.apply(q4, k4, v4, ck, cv, g_slc, g_swa, g_cmp, cfg)
+        # the gate projection (nn.Linear(head_dim, 3), no activation) runs inside the fused node
+        o = _NSACore.apply(q4, k4, v4, ck, cv, self.gating.weight, self.gating.bias, cfg)
         return o.reshape(-1, *o.shape[-2:])

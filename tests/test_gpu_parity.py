@@ -342,6 +342,42 @@ def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window):
     nsa._lib.device_status()
 
 
+@pytest.mark.parametrize("D,rows", [(128, 4999), (64, 130)])
+def test_gate_projection_and_row_prepass(nsa, D, rows):
+    """nsa_gate_fwd / nsa_rowdot3 / nsa_gate_bwd against fp32 torch on the same bf16 inputs (nn.Linear(head_dim, 3) of
+    nsa/nsa.py:59,117 and its autograd)."""
+    L, P, S = nsa._lib.lib(), nsa._lib.ptr, nsa._lib.stream
+    gen = torch.Generator().manual_seed(5 + D)
+    q, do, o0, o1, o2, dq0 = (_r(torch.randn(rows, D, generator=gen)) for _ in range(6))
+    w = _r(torch.randn(3, D, generator=gen) * 0.1)
+    b = _r(torch.randn(3, generator=gen))
+    qd, dod, o0d, o1d, o2d, wd, bd = (_dev(x) for x in (q, do, o0, o1, o2, w, b))
+    g = [torch.empty(rows, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+    nsa._lib.check(L.nsa_gate_fwd(P(qd), P(wd), P(bd), P(g[0]), P(g[1]), P(g[2]), rows, D, S()), "gate_fwd")
+    ref_g = q @ w.t() + b
+    for x in range(3):
+        _close("gate %d" % x, g[x], ref_g[:, x], atol=1e-2)
+    delta = [torch.empty(rows, dtype=torch.float32, device=DEV) for _ in range(3)]
+    dg = [torch.empty(rows, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+    nsa._lib.check(L.nsa_rowdot3(P(o0d), P(o1d), P(o2d), P(dod), P(g[0]), P(g[1]), P(g[2]), P(delta[0]), P(delta[1]),
+                                 P(delta[2]), P(dg[0]), P(dg[1]), P(dg[2]), rows, D, S()), "rowdot3")
+    for x, o in enumerate((o0, o1, o2)):
+        rs = (o * do).sum(-1)
+        _close("dgate %d" % x, dg[x], rs, atol=6e-2, rtol=1e-2)
+        _close("delta %d" % x, delta[x], rs * g[x].float().cpu(), atol=1e-3, rtol=1e-3)
+    dqd = _dev(dq0).clone()
+    dw, db = torch.empty(3, D, dtype=torch.bfloat16, device=DEV), torch.empty(3, dtype=torch.bfloat16, device=DEV)
+    nb = L.nsa_gate_bwd_workspace_bytes(rows, D)
+    ws = torch.empty(nb, dtype=torch.uint8, device=DEV)
+    nsa._lib.check(L.nsa_gate_bwd(P(qd), P(dg[0]), P(dg[1]), P(dg[2]), P(wd), P(dqd), P(dw), P(db), P(ws), nb, rows, D,
+                                  S()), "gate_bwd")
+    dgf = torch.stack([x.float().cpu() for x in dg], -1)        # [rows, 3], the bf16 values the kernel read
+    _close("dq", dqd, dq0 + dgf @ w, atol=3e-2)
+    _close("dw", dw, dgf.t() @ q, atol=4e-2, scaled=True)
+    _close("db", db.view(1, 3), dgf.sum(0).view(1, 3), atol=4e-2, scaled=True)
+    nsa._lib.device_status()
+
+
 # ------------------------------------------------------------------------------------------------------
 # full-size properties (BASELINE.json config 2: B=4, T=8192, Hq=64, Hkv=4, D=128, top-16 of 64-key blocks)
 # ------------------------------------------------------------------------------------------------------
@@ -399,15 +435,15 @@ def test_query_shards_match_unsharded_run(nsa):
     Tc = (T - 32) // 16 + 1
     q, k, v = (_dev(_r(torch.randn(B, T, h, D, generator=gen))) for h in (Hq, Hkv, Hkv))
     ck, cv = (_dev(_r(torch.randn(B, Tc, Hkv, D, generator=gen) * 0.5)) for _ in range(2))
-    gates = [_dev(_r(torch.rand(B, T, Hq, generator=gen))) for _ in range(3)]
+    wg = _dev(_r(torch.randn(3, D, generator=gen) * 0.05))
+    bg = _dev(_r(torch.tensor([0.5, 0.4, 0.6])))
     do = _dev(_r(torch.randn(B, T, Hq, D, generator=gen)))
 
     def run(q0, Tq):
         sl = slice(q0, q0 + Tq)
-        leaves = [t.clone().requires_grad_(True) for t in (q[:, sl].contiguous(), k, v, ck, cv)]
-        g = [x[:, sl].contiguous() for x in gates]
+        leaves = [t.clone().requires_grad_(True) for t in (q[:, sl].contiguous(), k, v, ck, cv, wg, bg)]
         cfg = (16, 32, True, D ** -0.5, 5, 4, 0, n_sel, 64, window, q0)
-        o = _NSACore.apply(*leaves, *g, cfg)
+        o = _NSACore.apply(*leaves, cfg)
         o.backward(do[:, sl].contiguous())
         return o.detach(), [t.grad for t in leaves]
 
@@ -422,8 +458,9 @@ def test_query_shards_match_unsharded_run(nsa):
             s_ += g_.float()
     assert torch.equal(torch.cat([o_parts[c] for c in range(4)], 1), o_full)
     assert torch.equal(torch.cat([dq_parts[c] for c in range(4)], 1), g_full[0])
-    for name, s_, ref in zip(("dk", "dv", "dck", "dcv"), sums, g_full[1:]):
-        _close(name + " summed over shards", s_, ref, scaled=True)
+    for name, s_, ref in zip(("dk", "dv", "dck", "dcv", "d gating.weight", "d gating.bias"), sums, g_full[1:]):
+        _close(name + " summed over shards", s_.reshape(-1, s_.shape[-1]), ref.reshape(-1, ref.shape[-1]), atol=4e-2,
+               scaled=True)
     nsa._lib.device_status()
 
 
