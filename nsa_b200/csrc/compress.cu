@@ -258,17 +258,40 @@ __global__ void compress_dw_reduce_kernel(const float* __restrict__ ws, float* _
   dw[i] = s;
 }
 
-// dbias[o] = sum over all output rows of dY[row, o]; one CTA, fixed order
+// dbias[o] = sum over all output rows of dY[row, o]; one CTA, fixed order.  A thread owns 8 channels (one 16-byte
+// load per row) of every (blockDim / (D/8))-th row and keeps eight loads in flight.
 __global__ void compress_dbias_kernel(const bf16* __restrict__ dy, float* __restrict__ dbias, long long rows, int D) {
-  extern __shared__ float red[];
-  const int col = threadIdx.x % D, lane_r = threadIdx.x / D, nr = blockDim.x / D;
-  float s = 0.f;
-  for (long long r = lane_r; r < rows; r += nr) s += __bfloat162float(dy[r * D + col]);
-  red[threadIdx.x] = s;
+  extern __shared__ float red[];   // [nr][D]
+  const int cpr = D / 8;           // 16-byte chunks per row
+  const int cc = threadIdx.x % cpr, rl = threadIdx.x / cpr, nr = blockDim.x / cpr;
+  float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  constexpr int U = 8;
+  for (long long r0 = rl; r0 < rows; r0 += (long long)nr * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long r = r0 + (long long)u * nr;
+      v[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (r < rows) v[u] = *reinterpret_cast<const uint4*>(dy + r * D + cc * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        s[2 * k] += f.x;
+        s[2 * k + 1] += f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[rl * D + cc * 8 + k] = s[k];
   __syncthreads();
-  if (lane_r == 0) {
-    for (int k = 1; k < nr; ++k) s += red[k * D + col];
-    dbias[col] = s;
+  if (threadIdx.x < D) {
+    float t = 0.f;
+    for (int k = 0; k < nr; ++k) t += red[k * D + threadIdx.x];
+    dbias[threadIdx.x] = t;
   }
 }
 
@@ -314,8 +337,9 @@ int bwd(const CompressArgs& a, cudaStream_t s) {
     note_launches(2);
   }
   if (a.dbias) {
-    const int nt = 1024 / D * D;
-    compress_dbias_kernel<<<1, nt, nt * sizeof(float), s>>>(a.dy, a.dbias, (long long)a.total_out * a.H, D);
+    const int nt = 1024, nr = nt / (D / 8);
+    cudaFuncSetAttribute(compress_dbias_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, nr * D * (int)sizeof(float));
+    compress_dbias_kernel<<<1, nt, nr * D * sizeof(float), s>>>(a.dy, a.dbias, (long long)a.total_out * a.H, D);
     note_launches(1);
   }
   return (int)cudaGetLastError();
@@ -397,8 +421,9 @@ int bwd_static(const CompressArgs& a0, cudaStream_t s) {
     note_launches(2);
   }
   if (a.dbias) {
-    const int nt = 1024 / D * D;
-    compress_dbias_kernel<<<1, nt, nt * sizeof(float), s>>>(a.dy, a.dbias, (long long)a.total_out * a.H, D);
+    const int nt = 1024, nr = nt / (D / 8);
+    cudaFuncSetAttribute(compress_dbias_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, nr * D * (int)sizeof(float));
+    compress_dbias_kernel<<<1, nt, nr * D * sizeof(float), s>>>(a.dy, a.dbias, (long long)a.total_out * a.H, D);
     note_launches(1);
   }
   return (int)cudaGetLastError();

@@ -33,21 +33,61 @@ __device__ __forceinline__ int load_block_index(const void* idx, int idx64, long
   return (int)v;
 }
 
-// acc[16 x NK] += A[16 x D] * Tile[row0 .. row0+NK)[D]^T with the contraction step outermost: consecutive mma
-// instructions write different accumulators (NK/8 independent chains).
+// The ldmatrix / mma helpers below are written as volatile asm, so they execute in exactly the order given here: every
+// B fragment is fetched one group ahead of the mma instructions that use it.
+//
+// acc[16 x NK] += A[16 x D] * Tile[row0 .. row0+NK)[D]^T, contraction step outermost: the mma instructions of a step
+// write NK/8 different accumulators.
 template <int D, int NK>
 __device__ __forceinline__ void mma_a_bt_wide(float (&acc)[NK / 8][4], const uint32_t (&af)[D / 16][4], uint32_t base,
                                               uint32_t panel_bytes, int row0, int lane) {
   const int m = lane >> 3, rr = lane & 7;
+  constexpr int NG = NK / 16;   // ldmatrix.x4 per contraction step
+  uint32_t b[2][NG][4];
+  auto fetch = [&](int ks, uint32_t (&dst)[NG][4]) {
+#pragma unroll
+    for (int n2 = 0; n2 < NG; ++n2) {
+      const int row = row0 + n2 * 16 + (m >> 1) * 8 + rr;
+      ldsm_x4(tile_addr(base, panel_bytes, row, ks * 2 + (m & 1)), dst[n2][0], dst[n2][1], dst[n2][2], dst[n2][3]);
+    }
+  };
+  fetch(0, b[0]);
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
+    if (ks + 1 < D / 16) fetch(ks + 1, b[(ks + 1) & 1]);
 #pragma unroll
-    for (int n2 = 0; n2 < NK / 16; ++n2) {
-      const int row = row0 + n2 * 16 + (m >> 1) * 8 + rr;
-      uint32_t b0, b1, b2, b3;
-      ldsm_x4(tile_addr(base, panel_bytes, row, ks * 2 + (m & 1)), b0, b1, b2, b3);
-      mma_bf16(acc[2 * n2], af[ks], b0, b1);
-      mma_bf16(acc[2 * n2 + 1], af[ks], b2, b3);
+    for (int n2 = 0; n2 < NG; ++n2) {
+      mma_bf16(acc[2 * n2], af[ks], b[ks & 1][n2][0], b[ks & 1][n2][1]);
+      mma_bf16(acc[2 * n2 + 1], af[ks], b[ks & 1][n2][2], b[ks & 1][n2][3]);
+    }
+  }
+}
+
+// acc[16 x D] += P[16 x NK] * Tile[row0 .. row0+NK)[D], B fragments fetched four ldmatrix ahead.
+template <int D, int NK>
+__device__ __forceinline__ void mma_a_b_pipelined(float (&acc)[D / 8][4], const uint32_t (&pf)[NK / 16][4], uint32_t base,
+                                                  uint32_t panel_bytes, int row0, int lane) {
+  const int m = lane >> 3, rr = lane & 7;
+  constexpr int G = 4;                       // ldmatrix.x4 per group
+  constexpr int NGRP = (NK / 16) * (D / 16) / G;
+  uint32_t b[2][G][4];
+  auto fetch = [&](int grp, uint32_t (&dst)[G][4]) {
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      const int idx = grp * G + i, kk = idx / (D / 16), n2 = idx % (D / 16);
+      const int row = row0 + kk * 16 + (m & 1) * 8 + rr;
+      ldsm_x4_t(tile_addr(base, panel_bytes, row, n2 * 2 + (m >> 1)), dst[i][0], dst[i][1], dst[i][2], dst[i][3]);
+    }
+  };
+  fetch(0, b[0]);
+#pragma unroll
+  for (int grp = 0; grp < NGRP; ++grp) {
+    if (grp + 1 < NGRP) fetch(grp + 1, b[(grp + 1) & 1]);
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      const int idx = grp * G + i, kk = idx / (D / 16), n2 = idx % (D / 16);
+      mma_bf16(acc[2 * n2], pf[kk], b[grp & 1][i][0], b[grp & 1][i][1]);
+      mma_bf16(acc[2 * n2 + 1], pf[kk], b[grp & 1][i][2], b[grp & 1][i][3]);
     }
   }
 }
@@ -80,10 +120,18 @@ __device__ __forceinline__ Item decode_item(const SelArgs& a, long long idx, lon
   Item it;
   it.valid = idx < total;
   if (!it.valid) idx = 0;
-  const int hg = (int)(idx % HG);
-  it.tl = a.Tq - 1 - (int)((idx / HG) % a.Tq);
+  int hg;
+  if (total <= 0x7fffffffLL) {   // 32-bit divisions: the 64-bit ones cost hundreds of cycles per item
+    const unsigned i = (unsigned)idx, th = i / (unsigned)HG;
+    hg = (int)(i - th * (unsigned)HG);
+    it.b = (int)(th / (unsigned)a.Tq);
+    it.tl = a.Tq - 1 - (int)(th - (unsigned)it.b * (unsigned)a.Tq);
+  } else {
+    hg = (int)(idx % HG);
+    it.tl = a.Tq - 1 - (int)((idx / HG) % a.Tq);
+    it.b = (int)(idx / ((long long)HG * a.Tq));
+  }
   it.t = a.q0 + it.tl;
-  it.b = (int)(idx / ((long long)HG * a.Tq));
   it.hkv = hg / G16;
   it.row = ((long long)it.b * a.Tq + it.tl) * a.Hkv + it.hkv;
   it.qrow = ((long long)it.b * a.Tq + it.tl) * a.Hq + hg * 16;
@@ -148,7 +196,15 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
   const long long first = (long long)blockIdx.x * kWarps + cw;    // its items: first, first + step, ...
   const long long step = (long long)gridDim.x * kWarps;
   const int ring0 = cw * spw;                                     // first slot of its private ring
-  uint32_t it = 0;    // blocks through the ring so far
+  int rs = 0;         // ring position of the next block's K slot (V takes the one after) and its phase parity,
+  uint32_t rp = 0;    // stepped without divisions
+  auto ring_advance2 = [&]() {
+    rs += 2;
+    if (rs >= spw) {
+      rs -= spw;
+      rp ^= 1;
+    }
+  };
   uint32_t qn = 0;    // Q tiles staged so far
 
   if (warp >= kWarps) {
@@ -180,16 +236,22 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
         mask &= mask - 1;
         const int blk = __shfl_sync(0xffffffffu, ent, bit);
         if (lane < 2 * NP) {
-          const uint32_t pos = 2u * it + bkv;
-          const int stage = ring0 + pos % spw;
-          good = mbar_wait_abortable(empty_bar(stage), ((pos / spw) & 1) ^ 1, DEV_ERR_EMPTY_WAIT, abort_flag) ? 1 : 0;
+          // K takes the ring position `rs`, V the next one
+          int stage = rs;
+          uint32_t par = rp;
+          if (bkv && ++stage == spw) {
+            stage = 0;
+            par ^= 1;
+          }
+          stage += ring0;
+          good = mbar_wait_abortable(empty_bar(stage), par ^ 1, DEV_ERR_EMPTY_WAIT, abort_flag) ? 1 : 0;
           if (good) {
             if (bp == 0) mbar_expect_tx(full_bar(stage), slot_bytes);
             tma_load_4d(sbase + stage * slot_bytes + bp * panel_bytes, bkv ? &tmV : &tmK, full_bar(stage), bp * 64,
                         item.hkv, blk * BS, item.b);
           }
         }
-        ++it;
+        ring_advance2();
         if (!__all_sync(0xffffffffu, good)) return;
       }
     }
@@ -245,11 +307,18 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
         my_mask &= my_mask - 1;
         const int blk = __shfl_sync(0xffffffffu, my_ent, bit);
         const bool edge = blk * BS + BS - 1 > me.t;    // the block that contains the query's own position
-        const uint32_t kpos = 2u * it, vpos = kpos + 1;
-        const int kst = ring0 + kpos % spw, vst = ring0 + vpos % spw;
-        const uint32_t kbase = sbase + kst * slot_bytes, vbase = sbase + vst * slot_bytes;
-        ++it;
-        ok = ok && mbar_wait_abortable(full_bar(kst), (kpos / spw) & 1, DEV_ERR_FULL_WAIT, abort_flag);
+        const int kbar = ring0 + rs;
+        const uint32_t kpar = rp;
+        int vs = rs + 1;
+        uint32_t vpar = rp;
+        if (vs == spw) {
+          vs = 0;
+          vpar ^= 1;
+        }
+        const int vbar = ring0 + vs;
+        ring_advance2();
+        const uint32_t kbase = sbase + kbar * slot_bytes, vbase = sbase + vbar * slot_bytes;
+        ok = ok && mbar_wait_abortable(full_bar(kbar), kpar, DEV_ERR_FULL_WAIT, abort_flag);
         if constexpr (!BWD) {
           const int key0 = blk * BS + 2 * tq;  // key of sc[0][0]; sc[nt][c]: + 8*nt + (c&1)
           float sc[BS / 8][4];
@@ -257,7 +326,8 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
           for (int i = 0; i < BS / 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
           if (ok) mma_a_bt_wide<D, BS>(sc, qf, kbase, panel_bytes, 0, lane);
           __syncwarp();
-          if (lane == 0) mbar_arrive(empty_bar(kst));
+          if (lane == 0) mbar_arrive(empty_bar(kbar));
+          // maxima on the raw scores (the scale is positive: sel_block_supported), scale folded into the exponent's FMA
           float mx[2] = {-INFINITY, -INFINITY};
           if (edge) {
 #pragma unroll
@@ -265,37 +335,32 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
                 const int key = key0 + 8 * nt + (c & 1);
-                const float v = (key <= me.t) ? sc[nt][c] * sl2 : -INFINITY;
-                sc[nt][c] = v;
-                mx[c >> 1] = fmaxf(mx[c >> 1], v);
+                if (key > me.t) sc[nt][c] = -INFINITY;
+                mx[c >> 1] = fmaxf(mx[c >> 1], sc[nt][c]);
               }
           } else {
 #pragma unroll
             for (int nt = 0; nt < BS / 8; ++nt)
 #pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                const float v = sc[nt][c] * sl2;
-                sc[nt][c] = v;
-                mx[c >> 1] = fmaxf(mx[c >> 1], v);
-              }
+              for (int c = 0; c < 4; ++c) mx[c >> 1] = fmaxf(mx[c >> 1], sc[nt][c]);
           }
           float alpha[2];
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
-            const float mnew = fmaxf(m_run[rr], quad_max(mx[rr]));
+            const float mnew = fmaxf(m_run[rr], quad_max(mx[rr]) * sl2);
             const float muse = (mnew == -INFINITY) ? 0.f : mnew;
             alpha[rr] = ex2(m_run[rr] - muse);
             m_run[rr] = mnew;
-            float rs = 0.f;
+            float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-            for (int nt = 0; nt < BS / 8; ++nt)
-#pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                const float e = ex2(sc[nt][2 * rr + c] - muse);
-                sc[nt][2 * rr + c] = e;
-                rs += e;
-              }
-            l_run[rr] = l_run[rr] * alpha[rr] + rs;
+            for (int nt = 0; nt < BS / 8; ++nt) {
+              const float e0 = ex2(fmaf(sc[nt][2 * rr], sl2, -muse)), e1 = ex2(fmaf(sc[nt][2 * rr + 1], sl2, -muse));
+              sc[nt][2 * rr] = e0;
+              sc[nt][2 * rr + 1] = e1;
+              rs0 += e0;
+              rs1 += e1;
+            }
+            l_run[rr] = l_run[rr] * alpha[rr] + (rs0 + rs1);
           }
           // the accumulator is rescaled only when some row's maximum moved
           if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
@@ -309,12 +374,12 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
           }
           uint32_t pf[BS / 16][4];
           acc_to_a_frags<BS / 8>(pf, sc);
-          ok = ok && mbar_wait_abortable(full_bar(vst), (vpos / spw) & 1, DEV_ERR_FULL_WAIT, abort_flag);
-          if (ok) mma_a_b<D, BS>(acc, pf, vbase, panel_bytes, 0, lane);
+          ok = ok && mbar_wait_abortable(full_bar(vbar), vpar, DEV_ERR_FULL_WAIT, abort_flag);
+          if (ok) mma_a_b_pipelined<D, BS>(acc, pf, vbase, panel_bytes, 0, lane);
           __syncwarp();
-          if (lane == 0) mbar_arrive(empty_bar(vst));
+          if (lane == 0) mbar_arrive(empty_bar(vbar));
         } else {
-          ok = ok && mbar_wait_abortable(full_bar(vst), (vpos / spw) & 1, DEV_ERR_FULL_WAIT, abort_flag);
+          ok = ok && mbar_wait_abortable(full_bar(vbar), vpar, DEV_ERR_FULL_WAIT, abort_flag);
           constexpr int CK = 32;   // keys per pass: scores and dP of a pass stay in registers
 #pragma unroll
           for (int h = 0; h < BS / CK; ++h) {
@@ -331,7 +396,7 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
             }
             if (h == BS / CK - 1) {   // V is not needed any more
               __syncwarp();
-              if (lane == 0) mbar_arrive(empty_bar(vst));
+              if (lane == 0) mbar_arrive(empty_bar(vbar));
             }
 #pragma unroll
             for (int nt = 0; nt < CK / 8; ++nt)
@@ -344,10 +409,10 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
               }
             uint32_t dsf[CK / 16][4];
             acc_to_a_frags<CK / 8>(dsf, sc);
-            if (ok) mma_a_b<D, CK>(acc, dsf, kbase, panel_bytes, h * CK, lane);
+            if (ok) mma_a_b_pipelined<D, CK>(acc, dsf, kbase, panel_bytes, h * CK, lane);
           }
           __syncwarp();
-          if (lane == 0) mbar_arrive(empty_bar(kst));
+          if (lane == 0) mbar_arrive(empty_bar(kbar));
         }
       }
     }
@@ -432,7 +497,9 @@ int launch(const SelArgs& a, cudaStream_t s) {
 
 }  // namespace
 
-bool sel_block_supported(const SelArgs& a, int D) { return a.BS == BS && a.S <= 32 && (D == 128 || D == 64); }
+bool sel_block_supported(const SelArgs& a, int D) {
+  return a.BS == BS && a.S <= 32 && (D == 128 || D == 64) && a.scale > 0.f;
+}
 
 int launch_sel_block(const SelArgs& a, int D, bool bwd, cudaStream_t s) {
   if (D == 128) return bwd ? launch<128, true>(a, s) : launch<128, false>(a, s);
