@@ -145,6 +145,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, 0, 1);
       uint32_t c = 0, ic = 0;
       bool ok = true;
+      // operand descriptors are built once; an MMA then costs one 64-bit add per operand
+      const uint64_t dq_desc = umma_smem_desc(q_s, 0, 1024), ddo_desc = umma_smem_desc(do_s, 0, 1024);
+      const uint64_t dds_desc = umma_smem_desc(ds_s, 0, 1024);
+      const uint64_t dk_desc0 = umma_smem_desc(ring, 0, 1024), dk_desc1 = umma_smem_desc(ring + STAGE, 0, 1024);
+      const uint64_t dv_desc0 = umma_smem_desc(ring + TILE, 0, 1024), dv_desc1 = umma_smem_desc(ring + STAGE + TILE, 0, 1024);
+      const uint64_t dkmn_desc0 = umma_smem_desc(ring, PANEL, 1024), dkmn_desc1 = umma_smem_desc(ring + STAGE, PANEL, 1024);
       for (long long item = blockIdx.x; ok && item < total; item += gridDim.x, ++ic) {
         const int tile = ntile - 1 - (int)((item / HG) % ntile);
         const Sched sc = make_sched<MODE>(a, a.q0 + tile * kTok);
@@ -152,48 +158,65 @@ __global__ void __launch_bounds__(kThreads, 1)
         // dQ of the previous item must have been read, and dq_full must not complete twice unseen
         if (ok && ic > 0) ok = mbar_wait_abortable(dq_free, (ic - 1) & 1, 204, abort_flag);
         auto issue_sdp = [&](uint32_t cc) {
-          const uint32_t k_s = ring + (cc & 1) * STAGE, v_s = k_s + TILE;
+          const uint64_t dk = (cc & 1) ? dk_desc1 : dk_desc0, dv = (cc & 1) ? dv_desc1 : dv_desc0;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
-            umma_ss(tmem + 0, umma_smem_desc(q_s + off, 0, 1024), umma_smem_desc(k_s + off, 0, 1024), idesc_s, ks ? 1u : 0u);
+            umma_ss(tmem + 0, umma_desc_advance(dq_desc, off), umma_desc_advance(dk, off), idesc_s, ks ? 1u : 0u);
           }
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
-            umma_ss(tmem + 128, umma_smem_desc(do_s + off, 0, 1024), umma_smem_desc(v_s + off, 0, 1024), idesc_s, ks ? 1u : 0u);
+            umma_ss(tmem + 128, umma_desc_advance(ddo_desc, off), umma_desc_advance(dv, off), idesc_s, ks ? 1u : 0u);
           }
           umma_commit(sdp_full);
         };
-        if (ok && sc.n > 0) {
-          ok = mbar_wait_abortable(full0 + 8 * (c & 1), (c >> 1) & 1, 205, abort_flag);
-          if (ok && c > 0) ok = mbar_wait_abortable(sdp_free, (c - 1) & 1, 206, abort_flag);
-          if (ok) {
-            tc_fence_after();
-            issue_sdp(c);
+        // Event loop: S/dP of tile `ns` as soon as its stage has landed and the soft-max warps hold the previous
+        // tile's S/dP in registers; dQ of tile `nd` as soon as its dS tile is written -- whichever is ready first.
+        const uint32_t c0 = c;
+        int ns = 0, nd = 0;
+        uint64_t t_idle = 0;
+        while (ok && nd < sc.n) {
+          bool progressed = false;
+          if (ns < sc.n) {
+            const uint32_t cc = c0 + ns;
+            if (mbar_try(full0 + 8 * (cc & 1), (cc >> 1) & 1) && (cc == 0 || mbar_try(sdp_free, (cc - 1) & 1))) {
+              tc_fence_after();
+              issue_sdp(cc);
+              if (ns == sc.n - 1) umma_commit(q_free);   // every S/dP of the item issued: Q and dO may be reloaded after them
+              ++ns;
+              progressed = true;
+            }
           }
-        }
-        for (int i = 0; ok && i < sc.n; ++i, ++c) {
-          if (i + 1 < sc.n) {
-            ok = mbar_wait_abortable(full0 + 8 * ((c + 1) & 1), ((c + 1) >> 1) & 1, 205, abort_flag) &&
-                 mbar_wait_abortable(sdp_free, c & 1, 206, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            issue_sdp(c + 1);
-          } else {
-            umma_commit(q_free);   // every S/dP of the item has been issued: Q and dO tiles may be reloaded after them
-          }
-          ok = mbar_wait_abortable(ds_full, c & 1, 207, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t k_s = ring + (c & 1) * STAGE;
+          if (nd < ns) {
+            const uint32_t cc = c0 + nd;
+            if (mbar_try(ds_full, cc & 1)) {
+              tc_fence_after();
+              const uint64_t dkm = (cc & 1) ? dkmn_desc1 : dkmn_desc0;
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_ss(tmem + 256, umma_smem_desc(ds_s + (ks >> 2) * PANEL + (ks & 3) * 32, 0, 1024),
-                    umma_smem_desc(k_s + ks * 2048, PANEL, 1024), idesc_dq, (i | ks) ? 1u : 0u);
-          umma_commit(empty0 + 8 * (c & 1));
-          umma_commit(ds_free);
+              for (int ks = 0; ks < 8; ++ks)
+                umma_ss(tmem + 256, umma_desc_advance(dds_desc, (ks >> 2) * PANEL + (ks & 3) * 32),
+                        umma_desc_advance(dkm, ks * 2048), idesc_dq, (nd | ks) ? 1u : 0u);
+              umma_commit(empty0 + 8 * (cc & 1));
+              umma_commit(ds_free);
+              ++nd;
+              progressed = true;
+            }
+          }
+          if (progressed) {
+            t_idle = 0;
+          } else {   // bounded: the abort flag of another role, or ~2 s without progress, ends the loop
+            if (*abort_flag) ok = false;
+            const uint64_t now = global_timer_ns();
+            if (t_idle == 0) t_idle = now;
+            else if (now - t_idle > 2000000000ull) {
+              atomicCAS(&g_dev_error, 0, 205);
+              *abort_flag = 1;
+              ok = false;
+            }
+          }
         }
+        c = c0 + sc.n;
         if (sc.n == 0) umma_commit(q_free);
         umma_commit(dq_full);
       }

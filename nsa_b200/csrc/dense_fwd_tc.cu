@@ -165,46 +165,76 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);
       uint32_t c = 0, ic = 0, pc = 0;
       bool ok = true;
+      // operand descriptors are built once; an MMA then costs one 64-bit add per operand
+      const uint64_t dq_desc = umma_smem_desc(q_s, 0, 1024), dp_desc = umma_smem_desc(p_s, 0, 1024);
+      const uint64_t dk_desc0 = umma_smem_desc(ring, 0, 1024), dk_desc1 = umma_smem_desc(ring + STAGE, 0, 1024);
+      const uint64_t dv_desc0 = umma_smem_desc(ring + TILE, PANEL, 1024), dv_desc1 = umma_smem_desc(ring + STAGE + TILE, PANEL, 1024);
       for (long long item = blockIdx.x; ok && item < total; item += gridDim.x, ++ic) {
         const int tile = ntile - 1 - (int)((item / (a.Hq / 16)) % ntile);
         const Sched sc = make_sched<MODE>(a, a.q0 + tile * kTok);
         const int nt = sc.nA + sc.nB;
         ok = mbar_wait_abortable(q_full, ic & 1, 103, abort_flag);
-        auto finish = [&](uint32_t cc, int ii) {   // tile cc (item-local index ii) after its soft-max
-          const uint32_t st = cc & 1;
-          if (ii < sc.nAttn) {
-            if (!mbar_wait_abortable(p_full, pc & 1, 104, abort_flag)) return false;
-            tc_fence_after();
-            const uint32_t v_s = ring + st * STAGE + TILE;
+        // Event loop over the item's tiles: S of tile `ns` is issued as soon as its K/V stage has landed and its TMEM
+        // buffer has been read, P.V of tile `np` as soon as its P tile is written -- whichever is ready first.  A
+        // fixed order (S(i), then P.V(i-1)) left the tensor core idle: the stage of tile i+1 is only freed by
+        // P.V(i-1), so a thread blocked on that stage could not issue P.V(i) although its P tile was ready.
+        const uint32_t c0 = c;
+        int ns = 0, np = 0;
+        uint64_t t_idle = 0;
+        while (ok && np < nt) {
+          bool progressed = false;
+          if (ns < nt) {
+            const uint32_t cc = c0 + ns, st = cc & 1, ph = (cc >> 1) & 1;
+            if (mbar_try(full0 + 8 * st, ph) && mbar_try(s_free0 + 8 * st, ph ^ 1)) {
+              tc_fence_after();
+              const uint32_t k_s = ring + st * STAGE;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              umma_ss(tmem + 256, umma_smem_desc(p_s + (ks >> 2) * PANEL + (ks & 3) * 32, 0, 1024),
-                      umma_smem_desc(v_s + ks * 2048, PANEL, 1024), idesc_pv, (ii | ks) ? 1u : 0u);
-            umma_commit(empty0 + 8 * st);
-            umma_commit(p_free);
-            ++pc;
-          } else {
-            umma_commit(empty0 + 8 * st);
+              for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
+                umma_ss(tmem + st * 128, umma_desc_advance(dq_desc, off), umma_desc_advance(st ? dk_desc1 : dk_desc0, off),
+                        idesc_s, ks ? 1u : 0u);
+              }
+              umma_commit(s_full0 + 8 * st);
+              if (ns == nt - 1) umma_commit(q_free);
+              ++ns;
+              progressed = true;
+            }
           }
-          return true;
-        };
-        for (int i = 0; ok && i < nt; ++i, ++c) {
-          const uint32_t st = c & 1, ph = (c >> 1) & 1;
-          ok = mbar_wait_abortable(full0 + 8 * st, ph, 105, abort_flag) && mbar_wait_abortable(s_free0 + 8 * st, ph ^ 1, 106, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t k_s = ring + st * STAGE;
+          if (np < ns) {
+            const uint32_t cc = c0 + np, st = cc & 1;
+            if (np < sc.nAttn) {
+              if (mbar_try(p_full, pc & 1)) {
+                tc_fence_after();
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
-            umma_ss(tmem + st * 128, umma_smem_desc(q_s + off, 0, 1024), umma_smem_desc(k_s + off, 0, 1024), idesc_s,
-                    ks ? 1u : 0u);
+                for (int ks = 0; ks < 8; ++ks)
+                  umma_ss(tmem + 256, umma_desc_advance(dp_desc, (ks >> 2) * PANEL + (ks & 3) * 32),
+                          umma_desc_advance(st ? dv_desc1 : dv_desc0, ks * 2048), idesc_pv, (np | ks) ? 1u : 0u);
+                umma_commit(empty0 + 8 * st);
+                umma_commit(p_free);
+                ++pc;
+                ++np;
+                progressed = true;
+              }
+            } else {
+              umma_commit(empty0 + 8 * st);
+              ++np;
+              progressed = true;
+            }
           }
-          umma_commit(s_full0 + 8 * st);
-          if (i == nt - 1) umma_commit(q_free);
-          if (i > 0) ok = finish(c - 1, i - 1);
+          if (progressed) {
+            t_idle = 0;
+          } else {   // bounded: the abort flag of another role, or ~2 s without progress, ends the loop
+            if (*abort_flag) ok = false;
+            const uint64_t now = global_timer_ns();
+            if (t_idle == 0) t_idle = now;
+            else if (now - t_idle > 2000000000ull) {
+              atomicCAS(&g_dev_error, 0, 105);
+              *abort_flag = 1;
+              ok = false;
+            }
+          }
         }
-        if (ok && nt > 0) ok = finish(c - 1, nt - 1);
+        c = c0 + nt;
         if (nt == 0) umma_commit(q_free);
         // o_full must not complete twice before the soft-max warps have seen it once: items without P.V tiles do
         // not throttle this thread, so wait until the previous item's epilogue has been done
@@ -388,7 +418,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           named_bar_sync(1, kSoft);
           mx = fmaxf(mx, xb[(half ^ 1) * 128 + row]);
           ++xp;
-          const float mnew = fmaxf(m_run, mx);
+          // Lazy rescale: the reference maximum only follows the true maximum when that has grown by more than 2^8
+          // (log2 domain), so exponentials stay below 256 and the TMEM round trip that rescales O is rare.  Both
+          // threads of a row see the same mx and m_run and take the same decision.
+          const float mtrue = fmaxf(m_run, mx);
+          const float mnew = (mtrue > m_run + 8.f || m_run == -INFINITY) ? mtrue : m_run;
           const float muse = (mnew == -INFINITY) ? 0.f : mnew;
           const float alpha = ex2(m_run - muse);   // 0 when m_run = -inf
           float rs0 = 0.f, rs1 = 0.f;
