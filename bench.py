@@ -396,12 +396,18 @@ def run_gpu(args):
             "sel+swa_dkv(+reverse index)": 1.5 * (fm_loc["slc"] + fm_loc["swa"]), "cmp_dkv(+reduce)": 1.5 * fm_loc["cmp"],
             "compress_fwd(one of k,v)": fm_loc["comp"] / 2, "compress_bwd(one of k,v)": fm_loc["comp"],
         }
+        # DRAM traffic per launch of the kernels that can dominate: dram__bytes_read + write from one ncu capture of
+        # the B=1 case (profiles/ncu_sections_tcgen05_and_sel_kernels_B1_T8192.md), which grows in proportion to the
+        # number of sequences (every sequence's K/V stays in L2, q/dO/o/dq are streamed once)
+        ncu_mb_per_seq = {"sel_fwd": 237, "sel_dq": 376, "sel+swa_dkv(+reverse index)": 875, "cmp_attn_fwd+select": 224,
+                          "swa_fwd": 243, "swa_dq": 393, "cmp_dq": 375, "cmp_dkv(+reduce)": 279}
         dom = max((n for n in kern if n in kflops), key=lambda n: kern[n])
         achieved = kflops[dom] / (kern[dom] * 1e-3) / 1e12
         peak = peaks["tf_sustained"]
         roof = {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 2), "peak": peak, "unit": "TFLOP/s",
                 "frac": round(achieved / peak, 4), "peak_source": peaks["source"] + " (sustained bf16 GEMM)",
-                "traffic": None, "ms_per_launch": round(kern[dom], 3),
+                "traffic": (ncu_mb_per_seq[dom] * 1e6 * Bl) if dom in ncu_mb_per_seq else None,
+                "traffic_source": "ncu capture at B=1 x sequences per rank", "ms_per_launch": round(kern[dom], 3),
                 "algorithmic_flops_per_launch": kflops[dom]}
         cb = None
         if world == 1 and not args.no_cpu:
