@@ -251,6 +251,27 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
     return out, keys_per_seq_head
 
 
+def bind_to_gpu_numa_node(local):
+    """Best effort: run this process (and so first-touch its pinned host buffers) on the CPU cores NVML reports as
+    local to the GPU, so host<->device copies do not cross the socket interconnect.  Changes only this process's CPU
+    affinity; skipped when NVML or the cores are not available.  Returns a short description for the JSON line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        both = near & allowed
+        if both and both != allowed:
+            os.sched_setaffinity(0, both)
+            return "bound to %d GPU-local cores of %d allowed" % (len(both), len(allowed))
+        return "all %d allowed cores are %s" % (len(allowed), "GPU-local" if both else "remote from the GPU")
+    except Exception as e:   # no NVML, no permission: leave the affinity alone
+        return "unchanged (%s)" % type(e).__name__
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -260,6 +281,7 @@ def run_gpu(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    numa = bind_to_gpu_numa_node(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -423,6 +445,7 @@ def run_gpu(args):
                        "selection": "indices produced by the fused top-16 of the step itself (oracle-style scoring)"},
             "tflops_algorithmic": fm_nom["total"] / (ms_step * 1e-3) / 1e12,
             "tflops_frac_of_sustained_peak": fm_nom["total"] / (ms_step * 1e-3) / 1e12 / world / peaks["tf_sustained"],
+            "host_affinity": numa,
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
                     "d2h_bytes_per_step": d2h * world, "ms_per_step": ms_e2e},
             "gpu_launches": int(launches[1] - launches[0]),

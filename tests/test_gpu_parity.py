@@ -464,6 +464,36 @@ def test_query_shards_match_unsharded_run(nsa):
     nsa._lib.device_status()
 
 
+def test_module_step_is_bit_reproducible(nsa):
+    """Twelve forward + backward passes of the module on the same inputs must agree bit for bit (no atomics, no
+    scheduling-dependent result).  The module's own selection leaves many queries with zero to two visible blocks,
+    which is the case that exposed a stale-tile race in the selected-attention producer/consumer hand-over."""
+    torch.manual_seed(0)
+    B, T, Hq, Hkv, D, S, W = 2, 1024, 32, 2, 128, 4, 128
+    q = torch.randn(B * T, Hq, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B * T, Hkv, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B * T, Hkv, D, device=DEV, dtype=torch.bfloat16)
+    do = torch.randn(B * T, Hq, D, device=DEV, dtype=torch.bfloat16)
+    mod = nsa.NSAAttention(D, True, None, 0.0, selected_block_count=S, sliding_window=W, device=DEV, dtype=torch.bfloat16)
+    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
+    ref = None
+    for it in range(12):
+        qd, kd, vd = (x.clone().requires_grad_(True) for x in (q, k, v))
+        for p in mod.parameters():
+            p.grad = None
+        out = mod(qd, kd, vd, cu, T)
+        out.backward(do)
+        torch.randn(1 << (10 + it), device=DEV).sum()           # unrelated work of varying length between passes
+        cur = {"out": out.detach(), "dq": qd.grad, "dk": kd.grad, "dv": vd.grad}
+        cur.update({"d " + n: p.grad.clone() for n, p in mod.named_parameters()})
+        if ref is None:
+            ref = {n: t.clone() for n, t in cur.items()}
+        else:
+            for n in cur:
+                assert torch.equal(cur[n], ref[n]), "%s differs between pass 0 and pass %d" % (n, it)
+    nsa._lib.device_status()
+
+
 def test_decode_rows_match_oracle(nsa):
     """One new token per sequence against a packed K/V cache of ragged lengths (BASELINE config 5's shape in small)."""
     from nsa_b200.decode import compress_cache, nsa_decode
