@@ -142,7 +142,8 @@ def _rand_indices(B, T, H, S, BS, gen, poison=True):
 
 @pytest.mark.parametrize("D,BS,S,Hq,Hkv,T,window", [(128, 64, 4, 32, 2, 384, 100), (64, 32, 5, 16, 1, 200, 0),
                                                     (128, 16, 3, 16, 1, 130, 33), (64, 64, 6, 32, 2, 300, 0),
-                                                    (128, 64, 20, 16, 1, 450, 0), (64, 64, 36, 16, 1, 2400, 0)])
+                                                    (128, 64, 20, 16, 1, 450, 0), (64, 64, 36, 16, 1, 2400, 0),
+                                                    (128, 64, 4, 32, 1, 300, 64)])   # last: 32 query heads per KV head
 def test_selection_and_window_fwd_bwd(nsa, D, BS, S, Hq, Hkv, T, window):
     gen = torch.Generator().manual_seed(1234 + D + BS)
     B = 2 if T < 1000 else 1     # the 36-selection case (general kernel at 64-key blocks) is long: one sequence
