@@ -14,8 +14,8 @@ the public API from pinned host buffers with the copies timed (`e2e`), the domin
 (`roofline`, timed with CUDA events inside this run), a per-kernel breakdown, the clocks sampled under load
 and the CPU baseline (the oracle restatement of the reference's naive torch path on the host cores).
 
-`--impl reference` times that CPU restatement alone (the reference itself is Python under /root/reference,
-which does not exist on the GPU box; it has no compiled artefact that could travel).
+`--impl reference` times that CPU restatement alone (the reference itself is a Python/Triton source tree that is
+not present where this runs; it has no compiled artefact that could travel).
 """
 import argparse
 import json

@@ -110,7 +110,7 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
 size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS);
 
 /* ---- query shards (context parallelism) -------------------------------------------------------------
- * No counterpart in the reference (it is single-GPU, SURVEY of its tests shows no distributed code).  The four
+ * No counterpart in the reference (it is single-GPU: neither its modules nor its tests hold distributed code).  The four
  * attention entry points again, for a rank that owns only the queries q0 .. q0+Tq-1 of a T-token sequence while
  * holding the whole K/V (and compressed K/V): every q-indexed tensor (q, o, lse, gates, indices, dout, delta, dq,
  * sel_idx, sel_scores) has Tq rows per batch, row i being sequence position q0+i; k, v, ck, cv, dk, dv, dck, dcv
@@ -142,7 +142,10 @@ int nsa_sel_swa_bwd_sharded(const void* q, const void* k, const void* v, const v
  * K/V cache.  q, o and the scratch o_cmp / o_slc / o_swa [nseq,Hq,D]; k, v [sum L,Hkv,D]; ck, cv
  * [sum Tc,Hkv,D] = the compressed cache (nsa_compress_fwd with the Conv1d length rule); cu_k, cu_c: HOST int32
  * [nseq+1]; gates [nseq,Hq] (NULL = 1); lse fp32 [3,nseq,Hq] and idx int32 [nseq,Hkv,n_sel] receive the
- * branch log-sum-exps and the selected blocks.  Needs head_dim 128, 64-key blocks, stride 16 / block 32. */
+ * branch log-sum-exps and the selected blocks.  Needs head_dim 128, 64-key blocks, stride 16 / block 32.
+ * The sequences' kernels (a few CTAs each) are spread over a per-device pool of eight internal non-blocking streams
+ * that fork from and join `stream` through events: no host synchronisation, and all work is ordered after what was
+ * on `stream` before the call and before what is enqueued on it afterwards. */
 int nsa_decode_fwd(const void* q, const void* k, const void* v, const void* ck, const void* cv, const int32_t* cu_k,
                    const int32_t* cu_c, const void* g_slc, const void* g_swa, const void* g_cmp, void* o, void* o_cmp,
                    void* o_slc, void* o_swa, float* lse, int32_t* idx, int nseq, int Hq, int Hkv, int D, int block,
