@@ -431,6 +431,11 @@ def run_gpu(args):
                 "traffic": (ncu_mb_per_seq[dom] * 1e6 * Bl) if dom in ncu_mb_per_seq else None,
                 "traffic_source": "ncu capture at B=1 x sequences per rank", "ms_per_launch": round(kern[dom], 3),
                 "algorithmic_flops_per_launch": kflops[dom]}
+        if dom in ("sel_fwd", "sel_dq"):
+            # these kernels run mma.sync (16 query rows per KV head cannot fill a tcgen05 tile); 574 TFLOP/s is the
+            # m16n8k16 bf16 rate measured on this GPU type with every scheduler issuing back to back
+            roof["pipe"] = "mma.sync"
+            roof["frac_of_mma_sync_peak"] = round(achieved / 574.0, 4)
         cb = None
         if world == 1 and not args.no_cpu:
             cb, _ = cpu_step(1024, 1, 0)
