@@ -236,10 +236,12 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
         mask &= mask - 1;
         const int blk = __shfl_sync(0xffffffffu, ent, bit);
         if (lane < 2 * NP) {
-          // K takes the ring position `rs`, V the next one
+          // Forward: K takes the ring position `rs`, V the next one.  Backward: V first, then K -- V is released
+          // after dP, well before the block ends, and the slot freed early is the one the SECOND tensor of the next
+          // block reuses (three slots per ring), so both tensors of the next block land while this one computes.
           int stage = rs;
           uint32_t par = rp;
-          if (bkv && ++stage == spw) {
+          if ((BWD ? !bkv : bkv) && ++stage == spw) {
             stage = 0;
             par ^= 1;
           }
@@ -307,15 +309,18 @@ __global__ void __launch_bounds__(2 * kWarps * 32, 1)
         my_mask &= my_mask - 1;
         const int blk = __shfl_sync(0xffffffffu, my_ent, bit);
         const bool edge = blk * BS + BS - 1 > me.t;    // the block that contains the query's own position
-        const int kbar = ring0 + rs;
-        const uint32_t kpar = rp;
-        int vs = rs + 1;
-        uint32_t vpar = rp;
-        if (vs == spw) {
-          vs = 0;
-          vpar ^= 1;
+        // ring positions of the block's two tensors: K then V in the forward, V then K in the backward (see the producer)
+        const int first_bar = ring0 + rs;
+        const uint32_t first_par = rp;
+        int ss = rs + 1;
+        uint32_t second_par = rp;
+        if (ss == spw) {
+          ss = 0;
+          second_par ^= 1;
         }
-        const int vbar = ring0 + vs;
+        const int second_bar = ring0 + ss;
+        const int kbar = BWD ? second_bar : first_bar, vbar = BWD ? first_bar : second_bar;
+        const uint32_t kpar = BWD ? second_par : first_par, vpar = BWD ? first_par : second_par;
         ring_advance2();
         const uint32_t kbase = sbase + kbar * slot_bytes, vbase = sbase + vbar * slot_bytes;
         ok = ok && mbar_wait_abortable(full_bar(kbar), kpar, DEV_ERR_FULL_WAIT, abort_flag);
