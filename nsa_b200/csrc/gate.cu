@@ -247,9 +247,14 @@ __global__ void gate_reduce_kernel(const float* __restrict__ part, int nblk, int
     db[i - 3 * D] = __float2bfloat16(s);
 }
 
-int stream_grid(long long rows, int rows_per_block) {
-  const long long want = (rows + 4 * rows_per_block - 1) / (4 * rows_per_block);
-  const long long cap = (long long)num_sms() * 8;
+// Grid of a grid-stride streaming kernel: a whole number of resident waves (SMs x resident blocks per SM, from the
+// occupancy calculator), so no partial last wave; fewer blocks when there are fewer rows than that.
+template <typename K>
+int stream_grid(K kernel, long long rows, int rows_per_block) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGateThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+  const long long want = (rows + rows_per_block - 1) / rows_per_block;
+  const long long cap = (long long)num_sms() * per_sm;
   return (int)(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
@@ -259,9 +264,9 @@ int launch_gate_fwd(const bf16* q, const bf16* w, const bf16* bias, bf16* g0, bf
                     cudaStream_t s) {
   if (rows <= 0) return 0;
   if (D == 128)
-    gate_fwd_kernel<128><<<stream_grid(rows, 16), kGateThreads, 0, s>>>(q, w, bias, g0, g1, g2, rows);
+    gate_fwd_kernel<128><<<stream_grid(gate_fwd_kernel<128>, rows, 16), kGateThreads, 0, s>>>(q, w, bias, g0, g1, g2, rows);
   else if (D == 64)
-    gate_fwd_kernel<64><<<stream_grid(rows, 32), kGateThreads, 0, s>>>(q, w, bias, g0, g1, g2, rows);
+    gate_fwd_kernel<64><<<stream_grid(gate_fwd_kernel<64>, rows, 32), kGateThreads, 0, s>>>(q, w, bias, g0, g1, g2, rows);
   else {
     set_error("head_dim %d not supported (64 or 128)", D);
     return -2;
@@ -283,9 +288,9 @@ int launch_rowdot3(const bf16* const o[3], const bf16* dout, const bf16* const g
   a.dout = dout;
   a.rows = rows;
   if (D == 128)
-    rowdot3_kernel<128><<<stream_grid(rows, 16), kGateThreads, 0, s>>>(a);
+    rowdot3_kernel<128><<<stream_grid(rowdot3_kernel<128>, rows, 16), kGateThreads, 0, s>>>(a);
   else if (D == 64)
-    rowdot3_kernel<64><<<stream_grid(rows, 32), kGateThreads, 0, s>>>(a);
+    rowdot3_kernel<64><<<stream_grid(rowdot3_kernel<64>, rows, 32), kGateThreads, 0, s>>>(a);
   else {
     set_error("head_dim %d not supported (64 or 128)", D);
     return -2;
@@ -295,15 +300,19 @@ int launch_rowdot3(const bf16* const o[3], const bf16* dout, const bf16* const g
 }
 
 // workspace: one partial of 3*D+4 floats per block
+static int gate_bwd_grid(long long rows, int D) {
+  return D == 128 ? stream_grid(gate_bwd_kernel<128>, rows, 16) : stream_grid(gate_bwd_kernel<64>, rows, 32);
+}
+
 long long gate_bwd_workspace_bytes(long long rows, int D) {
-  const int grid = stream_grid(rows, D == 128 ? 16 : 32);
+  const int grid = gate_bwd_grid(rows, D);
   return (long long)grid * (3 * D + 4) * 4;
 }
 
 int launch_gate_bwd(const bf16* q, const bf16* dg0, const bf16* dg1, const bf16* dg2, const bf16* w, bf16* dq, bf16* dw,
                     bf16* db, float* workspace, long long rows, int D, cudaStream_t s) {
   if (rows <= 0) return 0;
-  const int grid = stream_grid(rows, D == 128 ? 16 : 32);
+  const int grid = gate_bwd_grid(rows, D);
   if (D == 128)
     gate_bwd_kernel<128><<<grid, kGateThreads, 0, s>>>(q, dg0, dg1, dg2, w, dq, workspace, rows);
   else if (D == 64)
