@@ -455,7 +455,11 @@ int nsa_decode_fwd(const void* q, const void* k, const void* v, const void* ck, 
   cudaEvent_t fork, join[kDecodeStreams];
   if (cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) != cudaSuccess) return fail(-40, "nsa_decode_fwd: event creation failed");
   for (int s = 0; s < nstream; ++s)
-    if (cudaEventCreateWithFlags(&join[s], cudaEventDisableTiming) != cudaSuccess) return fail(-40, "nsa_decode_fwd: event creation failed");
+    if (cudaEventCreateWithFlags(&join[s], cudaEventDisableTiming) != cudaSuccess) {
+      for (int u = 0; u < s; ++u) cudaEventDestroy(join[u]);
+      cudaEventDestroy(fork);
+      return fail(-40, "nsa_decode_fwd: event creation failed");
+    }
   cudaEventRecord(fork, user);
   for (int s = 0; s < nstream; ++s) cudaStreamWaitEvent(pool[s], fork, 0);
   int err = 0;
