@@ -247,6 +247,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       const float del = a.delta[qrow];
       const float gv = a.gate ? __bfloat162float(a.gate[qrow]) : 1.f;
       const bool dead = !live || !(lse2 > -INFINITY);
+      // the row's previous dq (accumulate mode) is fetched now, so its latency hides behind the tile loop instead of
+      // stalling the epilogue (measured: ~1000 of ~5000 cycles per tile)
+      uint4 outv[8];
+      bf16* dst = a.dq + qrow * D + half * 64;
+      if (a.accumulate && live) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) outv[e] = reinterpret_cast<const uint4*>(dst)[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) outv[e] = make_uint4(0u, 0u, 0u, 0u);
+      }
       for (int i = 0; i < sc.n; ++i, ++c) {
         const int j0 = (sc.first + i) * 128 + half * 64;
         ok = mbar_wait_abortable(sdp_full, c & 1, 208, abort_flag) && ok;
@@ -303,16 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       // ---- epilogue: dq = scale * dQ (+ previous contents) --------------------------------------------
       ok = mbar_wait_abortable(dq_full, ic & 1, 210, abort_flag) && ok;
       tc_fence_after();
-      uint4 outv[8];
       __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(outv);
-      bf16* dst = a.dq + qrow * D + half * 64;
-      if (a.accumulate && live) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) outv[e] = reinterpret_cast<const uint4*>(dst)[e];
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) outv[e] = make_uint4(0u, 0u, 0u, 0u);
-      }
       if (sc.n > 0) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
