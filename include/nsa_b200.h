@@ -61,7 +61,9 @@ size_t nsa_compress_bwd_workspace_bytes(int nseq, int H, int D, int block);
  * the allocator): the fp32 partials of the dW reduction go to a 16 MiB device array built into the library, so
  * there is no workspace argument and the call itself never allocates.  Limit: block*D*D <= 4 Mi floats (for
  * D = 128 that is block <= 256); larger shapes are rejected with a negative code and must use nsa_compress_bwd.
- * The first call on a device looks up the array's device address; make that call before any stream capture.
+ * The first call on a device looks up the array's device address; make that call before any stream capture.  The
+ * array used is the one of the device that is CURRENT when the call is made (cudaGetDevice), not of the device the
+ * stream belongs to: set the device before calling, as for every other entry point.
  * All calls share the one array and leave their partials in it (each call overwrites what it uses, nothing has
  * to be cleared), so two calls whose kernels could overlap on the GPU (different streams) race: serialise them. */
 int nsa_compress_bwd_noalloc(const void* x, const void* w, const void* dy, void* dx, float* dw, float* dbias,

@@ -141,6 +141,8 @@ int nsa_compress_bwd(const void* x, const void* w, const void* dy, void* dx, flo
                      size_t ws_bytes, const int32_t* cu_in, const int32_t* cu_out, int nseq, int H, int D, int block,
                      int stride, int max_in, int total_out, void* stream) {
   if (!x || !w || !dy || !cu_in || !cu_out) return fail(-1, "nsa_compress_bwd: null pointer");
+  if (nseq <= 0 || H <= 0) return fail(-1, "nsa_compress_bwd: empty shape");
+  if (D != 64 && D != 128) return fail(-2, "nsa_compress_bwd: head_dim %d not supported (64 or 128)", D);
   if (stride <= 0 || block <= 0 || block % stride) return fail(-4, "nsa_compress_bwd: block must be a multiple of stride");
   if (dw && (!ws || ws_bytes < nsa_compress_bwd_workspace_bytes(nseq, H, D, block)))
     return fail(-6, "nsa_compress_bwd: workspace too small");

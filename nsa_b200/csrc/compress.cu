@@ -310,8 +310,10 @@ int fwd(const CompressArgs& a, cudaStream_t s) {
   return (int)cudaGetLastError();
 }
 
+// dX, dW (fp32 partials in a.ws, `nsplit` of them, then a fixed-order reduction) and dbias.  Shared by the entry point
+// that takes a caller workspace and the one that uses the library's fixed array.
 template <int D>
-int bwd(const CompressArgs& a, cudaStream_t s) {
+int bwd_common(const CompressArgs& a, int nsplit, cudaStream_t s) {
   cudaError_t e;
   if (a.dx) {
     const int smem = 2 * (64 * 128 + D * 128) + 1024;
@@ -330,8 +332,8 @@ int bwd(const CompressArgs& a, cudaStream_t s) {
     auto kern = compress_dw_kernel<D>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    const int nsplit = a.nseq * a.H < kDwSplit ? a.nseq * a.H : kDwSplit;
-    kern<<<dim3(a.l, nsplit), D * 2, smem, s>>>(a, nsplit);
+    // every (j, split) CTA overwrites its whole [D x D] partial, so nothing in the workspace needs clearing
+    kern<<<dim3(a.l, (unsigned)nsplit), D * 2, smem, s>>>(a, nsplit);
     const long long n = (long long)a.l * D * D;
     compress_dw_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a.ws, a.dw, n, nsplit);
     note_launches(2);
@@ -343,6 +345,11 @@ int bwd(const CompressArgs& a, cudaStream_t s) {
     note_launches(1);
   }
   return (int)cudaGetLastError();
+}
+
+template <int D>
+int bwd(const CompressArgs& a, cudaStream_t s) {
+  return bwd_common<D>(a, a.nseq * a.H < kDwSplit ? a.nseq * a.H : kDwSplit, s);
 }
 
 
@@ -389,44 +396,18 @@ static int static_scratch(float** out) {
 template <int D>
 int bwd_static(const CompressArgs& a0, cudaStream_t s) {
   CompressArgs a = a0;
-  cudaError_t e;
-  if (a.dx) {
-    const int smem = 2 * (64 * 128 + D * 128) + 1024;
-    auto kern = compress_dx_kernel<D>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    const int nchunk = (a.max_in + a.d - 1) / a.d;
-    const dim3 grid((nchunk + 63) / 64, a.nseq * a.H, a.d);
-    if (a.max_in > 0) {
-      kern<<<grid, 128, smem, s>>>(a);
-      note_launches(1);
-    }
-  }
+  long long nsplit = 1;
   if (a.dw) {
     const long long per_split = (long long)a.l * D * D;
-    long long nsplit = kStaticScratchFloats / per_split;          // >= 1, checked by the caller
+    nsplit = kStaticScratchFloats / per_split;          // >= 1, checked by the caller
     if (nsplit > (long long)a.nseq * a.H) nsplit = (long long)a.nseq * a.H;
     if (nsplit > kDwSplit) nsplit = kDwSplit;
     float* scratch = nullptr;
     const int rc = static_scratch(&scratch);
     if (rc) return rc;
     a.ws = scratch;
-    const int smem = 2 * 2 * 64 * 128 * (D / 64) + 1024;
-    auto kern = compress_dw_kernel<D>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    // every (j, split) CTA overwrites its whole [D x D] partial, so nothing in the array needs clearing
-    kern<<<dim3(a.l, (unsigned)nsplit), D * 2, smem, s>>>(a, (int)nsplit);
-    compress_dw_reduce_kernel<<<(unsigned)((per_split + 255) / 256), 256, 0, s>>>(a.ws, a.dw, per_split, (int)nsplit);
-    note_launches(2);
   }
-  if (a.dbias) {
-    const int nt = 1024, nr = nt / (D / 8);
-    cudaFuncSetAttribute(compress_dbias_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, nr * D * (int)sizeof(float));
-    compress_dbias_kernel<<<1, nt, nr * D * sizeof(float), s>>>(a.dy, a.dbias, (long long)a.total_out * a.H, D);
-    note_launches(1);
-  }
-  return (int)cudaGetLastError();
+  return bwd_common<D>(a, (int)nsplit, s);
 }
 
 }  // namespace

@@ -129,11 +129,13 @@ def topn_blocks(scores: torch.Tensor, n: int) -> torch.Tensor:
 
 
 def cmp_attention(q: torch.Tensor, ck: torch.Tensor, cv: torch.Tensor, stride: int, block: int,
-                  causal: bool = True, scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                  causal: bool = True, scale: Optional[float] = None, q_pos=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Compressed attention.  o = softmax(scale * q.ck^T + mask) . cv, where with ``causal`` the
     compressed position j is visible to query t iff t >= j*stride + block; rows with no visible
     position give 0.  nsa/torch_attention.py:66-163 with the mask of :42-43.
-    Returns (o [B,T,Hq,D] fp32, lse [B,T,Hq] natural log of the scaled row sums; -inf if empty)."""
+    Returns (o [B,T,Hq,D] fp32, lse [B,T,Hq] natural log of the scaled row sums; -inf if empty).
+    ``q_pos`` (optional, [T]) gives the sequence positions of the query rows when q holds only some
+    rows of the sequence (row-chunked checks at full size)."""
     B, T, Hq, D = q.shape
     Tc, Hk = ck.shape[1], ck.shape[2]
     if scale is None:
@@ -143,7 +145,7 @@ def cmp_attention(q: torch.Tensor, ck: torch.Tensor, cv: torch.Tensor, stride: i
     cvr = cv.float().repeat_interleave(g, dim=2) if g > 1 else cv.float()
     s = torch.einsum("bthd,bshd->bhts", q.float(), ckr) * scale
     if causal:
-        row = torch.arange(T).unsqueeze(1)
+        row = (torch.arange(T) if q_pos is None else q_pos).unsqueeze(1)
         col = torch.arange(Tc).unsqueeze(0)
         masked = col * stride + block > row
         s = s.masked_fill(masked, float("-inf"))
@@ -217,9 +219,16 @@ def selected_attention(q, k, v, block_indices, block_counts=None, block_size: in
     return o, lse
 
 
-def sliding_window_attention(q, k, v, window: int, scale: Optional[float] = None, chunk: int = 256):
+def sliding_window_attention(q, k, v, window: int, scale: Optional[float] = None, chunk: int = 256, q0: int = 0):
     """Query t attends keys max(0, t-window+1) .. t.  tests/test_parallel_nsa.py:147-156 and
-    nsa/selection_attn.py:484-511.  Returns (o fp32 [B,T,Hq,D], lse fp32 [B,T,Hq])."""
+    nsa/selection_attn.py:484-511.  Returns (o fp32 [B,T,Hq,D], lse fp32 [B,T,Hq]).
+    With ``q0`` the rows of q are the sequence positions q0 .. q0+T-1 (k, v hold the whole sequence)."""
+    if q0:
+        k0 = max(0, q0 - window + 1)
+        n = q.shape[1]
+        pad = q.new_zeros(q.shape[0], q0 - k0, q.shape[2], q.shape[3])
+        o, lse = sliding_window_attention(torch.cat([pad, q], 1), k[:, k0:q0 + n], v[:, k0:q0 + n], window, scale, chunk)
+        return o[:, q0 - k0:], lse[:, q0 - k0:]
     B, T, Hq, D = q.shape
     Hkv = k.shape[2]
     G = Hq // Hkv

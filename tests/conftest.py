@@ -4,7 +4,7 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-for p in (ROOT, os.path.join(ROOT, "tests", "golden")):
+for p in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "tests", "golden")):
     if p not in sys.path:
         sys.path.insert(0, p)
 
@@ -25,3 +25,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter, exitstatus, config):
+    """Per-tensor error figures collected by the GPU parity tests (tests/parity_util.py)."""
+    try:
+        import parity_util
+    except Exception:
+        return
+    if parity_util.REPORT:
+        terminalreporter.section("parity report (unscaled errors beside the asserted tolerance)")
+        for line in parity_util.REPORT:
+            terminalreporter.write_line(line)

@@ -13,39 +13,16 @@ import torch
 
 import cases
 from oracle import nsa_oracle as O
+from parity_util import ATOL, RTOL, DEV, close as _close, dev as _dev, index_report
 
 pytestmark = pytest.mark.gpu
 
-ATOL, RTOL = 2e-2, 1e-2
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
-DEV = "cuda"
 
 
 def _gold(name):
     d = np.load(os.path.join(GOLD, name + ".npz"))
     return {k: torch.from_numpy(np.asarray(d[k])) for k in d.files}
-
-
-def _dev(x):
-    return x.to(DEV, torch.bfloat16)
-
-
-def _close(name, got, ref, atol=ATOL, rtol=RTOL, scaled=False):
-    """|got - ref| <= atol + rtol*|ref| elementwise.  With ``scaled`` (gradients that are sums over thousands of
-    (token, head) rows: dK, dV, dCK, dCV, weight gradients) every row (last dimension) of both sides is first divided
-    by max(1, RMS of the reference row): the bf16 rounding of the P and dS operands (the same roundings the
-    reference's kernels make) gives an error proportional to the energy summed into the row, not to the value of
-    the single element, so the absolute term is read on the unit-RMS row."""
-    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
-    assert got.shape == ref.shape, "%s: shape %s vs %s" % (name, tuple(got.shape), tuple(ref.shape))
-    assert not torch.isnan(got).any(), "%s: NaN in kernel output" % name
-    if scaled:
-        s = ref.square().mean(-1, keepdim=True).sqrt().clamp_min(1.0)
-        got, ref = got / s, ref / s
-    err = (got - ref).abs()
-    bad = err > atol + rtol * ref.abs()
-    assert not bad.any(), "%s: %d/%d outside tolerance, max abs err %.4g (ref max %.4g)" % (
-        name, int(bad.sum()), bad.numel(), float(err.max()), float(ref.abs().max()))
 
 
 @pytest.fixture(scope="module")
@@ -71,6 +48,7 @@ def test_cmp_attention_golden(nsa, name):
     _close("o", o, g["o"])
     sc = O.pooled_scores(c["q"], c["ck"], c["Hkv"], c["pool_kernel"], c["pool_stride"], c["pool_pad"])
     hard, soft = O.index_sets_match(idx.cpu(), sc, c["n"], gap=1e-3)
+    index_report("golden " + name, hard, soft, idx.numel() // idx.shape[-1])
     assert hard == 0, "%d rows select a block outside the 1e-3 waiver (%d rows differ at all)" % (hard, soft)
     o.backward(_dev(c["do"]))
     _close("dq", q.grad, g["dq"])
@@ -175,8 +153,10 @@ def test_selection_and_window_fwd_bwd(nsa, D, BS, S, Hq, Hkv, T, window):
     nsa._lib.device_status()
 
 
-@pytest.mark.parametrize("D,Hq,Hkv,T,block,stride", [(128, 32, 2, 520, 32, 16), (64, 16, 1, 333, 64, 16)])
-def test_cmp_attention_fwd_bwd(nsa, D, Hq, Hkv, T, block, stride):
+@pytest.mark.parametrize("D,Hq,Hkv,T,block,stride,causal", [(128, 32, 2, 520, 32, 16, True), (64, 16, 1, 333, 64, 16, True),
+                                                            (128, 32, 2, 520, 32, 16, False),
+                                                            (64, 16, 1, 333, 64, 16, False)])
+def test_cmp_attention_fwd_bwd(nsa, D, Hq, Hkv, T, block, stride, causal):
     gen = torch.Generator().manual_seed(77 + D)
     B, sel_block, n = 2, 64, 3
     Tc = (T - block) // stride + 1
@@ -186,12 +166,13 @@ def test_cmp_attention_fwd_bwd(nsa, D, Hq, Hkv, T, block, stride):
     do = _r(torch.randn(B, T, Hq, D, generator=gen))
     pk, ps, pp = sel_block // stride + 1, sel_block // stride, block // stride - 2
     qd, kd, vd = (_dev(x).requires_grad_(True) for x in (q, ck, cv))
-    o, idx = nsa.triton_attention.flash_attn_func(qd, kd, vd, stride, block, True, None, Hkv, pk, ps, pp, n)
+    o, idx = nsa.triton_attention.flash_attn_func(qd, kd, vd, stride, block, causal, None, Hkv, pk, ps, pp, n)
     qo, ko, vo = (x.clone().requires_grad_(True) for x in (q, ck, cv))
-    ro, _ = O.cmp_attention(qo, ko, vo, stride, block, True)
+    ro, _ = O.cmp_attention(qo, ko, vo, stride, block, causal)
     _close("o_cmp", o, ro)
     sc = O.pooled_scores(q, ck, Hkv, pk, ps, pp)
     hard, soft = O.index_sets_match(idx.cpu(), sc, n, gap=1e-3)
+    index_report("cmp D=%d T=%d causal=%s" % (D, T, causal), hard, soft, idx.numel() // idx.shape[-1])
     assert hard == 0, "%d rows select a block outside the 1e-3 waiver (%d differ)" % (hard, soft)
     o.backward(_dev(do))
     (ro * do).sum().backward()
@@ -200,7 +181,7 @@ def test_cmp_attention_fwd_bwd(nsa, D, Hq, Hkv, T, block, stride):
     _close("dcv", vd.grad, vo.grad, scaled=True)
     # the reference's repeated-head calling convention gives the same result
     o2, idx2 = nsa.triton_attention.flash_attn_func(_dev(q), _dev(ck).repeat_interleave(Hq // Hkv, 2),
-                                                    _dev(cv).repeat_interleave(Hq // Hkv, 2), stride, block, True, None,
+                                                    _dev(cv).repeat_interleave(Hq // Hkv, 2), stride, block, causal, None,
                                                     Hkv, pk, ps, pp, n)
     assert torch.equal(o2, o) and torch.equal(idx2, idx)
     nsa._lib.device_status()
@@ -255,12 +236,12 @@ def test_compression_varlen_fwd_bwd(nsa, D, H, block, stride, lens):
     nsa._lib.device_status()
 
 
-def _module_and_oracle(nsa, B, T, Hq, Hkv, D, n_sel, window, seed):
+def _module_and_oracle(nsa, B, T, Hq, Hkv, D, n_sel, window, seed, causal=True):
     gen = torch.Generator().manual_seed(seed)
     q = _r(torch.randn(B, T, Hq, D, generator=gen))
     k = _r(torch.randn(B, T, Hkv, D, generator=gen))
     v = _r(torch.randn(B, T, Hkv, D, generator=gen))
-    mod = nsa.NSAAttention(D, True, None, 0.0, selected_block_count=n_sel, sliding_window=window, device=DEV,
+    mod = nsa.NSAAttention(D, causal, None, 0.0, selected_block_count=n_sel, sliding_window=window, device=DEV,
                            dtype=torch.bfloat16)
     with torch.no_grad():
         for p in mod.parameters():
@@ -269,21 +250,13 @@ def _module_and_oracle(nsa, B, T, Hq, Hkv, D, n_sel, window, seed):
     return mod, q, k, v, gen
 
 
-def _oracle_module_forward(mod, q, k, v, indices, ck, cv, window):
-    """The oracle composition evaluated with the kernel's own compressed K/V (bf16) and selected indices, so the
-    comparison is not confounded by near-tie selections; both are checked separately against the oracle."""
-    wg, bg = mod.gating.weight.detach().float().cpu(), mod.gating.bias.detach().float().cpu()
-    o_cmp, _ = O.cmp_attention(q, ck, cv, mod.compression_stride, mod.compression_block, True)
-    o_slc, _ = O.selected_attention(q, k, v, indices, None, mod.selection_block_size)
-    o_swa, _ = O.sliding_window_attention(q, k, v, window)
-    gate = _r(q.float() @ wg.t() + bg)          # the module's gates are bf16 tensors
-    return o_slc * gate[..., 0:1] + o_swa * gate[..., 1:2] + o_cmp * gate[..., 2:3]
-
-
-@pytest.mark.parametrize("D,Hq,Hkv,T,n_sel,window", [(128, 32, 2, 1024, 4, 128), (64, 16, 1, 640, 3, 64)])
-def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window):
+@pytest.mark.parametrize("D,Hq,Hkv,T,n_sel,window,causal", [(128, 32, 2, 1024, 4, 128, True), (64, 16, 1, 640, 3, 64, True),
+                                                            (128, 32, 2, 1024, 4, 128, False)])
+def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window, causal):
+    """``causal`` is the module's constructor flag (default False in the reference, nsa/nsa.py:18): it only changes
+    the mask of the compressed branch; selected and sliding-window attention are causal either way."""
     B = 2
-    mod, q, k, v, gen = _module_and_oracle(nsa, B, T, Hq, Hkv, D, n_sel, window, seed=31 + D)
+    mod, q, k, v, gen = _module_and_oracle(nsa, B, T, Hq, Hkv, D, n_sel, window, seed=31 + D, causal=causal)
     cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
     qd, kd, vd = (_dev(x.reshape(B * T, *x.shape[2:])).requires_grad_(True) for x in (q, k, v))
     out = mod(qd, kd, vd, cu, T)
@@ -296,10 +269,11 @@ def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window):
     _close("cv", cvd, O.compress_conv(v, wv, bv, 32, 16))
     # stage 2: indices against the oracle scores on the kernel's compressed keys
     ck_b, cv_b = ckd.float().cpu(), cvd.float().cpu()
-    _, idx = nsa.triton_attention.flash_attn_func(qd.detach().view(B, T, Hq, D), ckd, cvd, 16, 32, True, None, Hkv, 5, 4,
-                                                  0, n_sel)
+    _, idx = nsa.triton_attention.flash_attn_func(qd.detach().view(B, T, Hq, D), ckd, cvd, 16, 32, causal, None, Hkv, 5,
+                                                  4, 0, n_sel)
     sc = O.pooled_scores(q, ck_b, Hkv, 5, 4, 0)
     hard, soft = O.index_sets_match(idx.cpu(), sc, n_sel, gap=1e-3)
+    index_report("module D=%d T=%d causal=%s" % (D, T, causal), hard, soft, idx.numel() // idx.shape[-1])
     assert hard == 0, "%d rows outside the waiver (%d differ)" % (hard, soft)
     # stage 3: the whole forward and backward with indices fixed to the kernel's
     qo, ko, vo = (x.clone().requires_grad_(True) for x in (q, k, v))
@@ -309,7 +283,7 @@ def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window):
     ck_o.retain_grad()
     wg_o = mod.gating.weight.detach().float().cpu().requires_grad_(True)
     bg_o = mod.gating.bias.detach().float().cpu().requires_grad_(True)
-    o_cmp, _ = O.cmp_attention(qo, ck_o, cv_o, 16, 32, True)
+    o_cmp, _ = O.cmp_attention(qo, ck_o, cv_o, 16, 32, causal)
     o_slc, _ = O.selected_attention(qo, ko, vo, idx.cpu(), None, 64)
     o_swa, _ = O.sliding_window_attention(qo, ko, vo, window)
     gate = qo @ wg_o.t() + bg_o
