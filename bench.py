@@ -11,8 +11,12 @@ gradients are all-reduced over NCCL inside the timed region.
 
 One JSON line is printed by rank 0: whole-job tokens/s with inputs resident in HBM (`value`), the same through
 the public API from pinned host buffers with the copies timed (`e2e`), the dominant kernel's roofline
-(`roofline`, timed with CUDA events inside this run), a per-kernel breakdown, the clocks sampled under load
-and the CPU baseline (the oracle restatement of the reference's naive torch path on the host cores).
+(`roofline`, timed with CUDA events inside this run), a per-kernel breakdown with one roofline entry per kernel
+(`kernel_rooflines`: tensor-pipe fraction on the keys actually visited; for the selected-attention kernels also the
+L2 -> SM gather rate against a measured gather ceiling), the clocks sampled under load, the CPU baseline (the oracle
+restatement of the reference's naive torch path on the host cores) and, under `secondary`, the other BASELINE.json
+configurations measured in the same process: `selection_microbench` (configs[1], N=1 only), `context` (configs[3] at
+the run's N) and `decode` (configs[4] at the run's N).
 
 `--impl reference` times that CPU restatement alone (the reference itself is a Python/Triton source tree that is
 not present where this runs; it has no compiled artefact that could travel).
@@ -32,6 +36,10 @@ if ROOT not in sys.path:
 CFG = dict(B=8, T=8192, Hq=64, Hkv=4, D=128, block=32, stride=16, sel_block=64, n_sel=16, window=512, seed=2)
 WORKLOAD = "configs[2]: NSAAttention module fwd+bwd bf16, B=8 T=8192 Hq=64 Hkv=4 D=128, cmp 32/16, sel 64 top-16, window 512"
 METRIC = "NSA fwd+bwd tokens/s"
+# ncu DRAM traffic per launch, MB per 8192-token sequence (see run_gpu), and the build it was captured from
+NCU_TRAFFIC_COMMIT = "86f9a53"
+NCU_MB_PER_SEQ = {"sel_fwd": 237, "sel_dq": 376, "sel+swa_dkv(+reverse index)": 875, "cmp_attn_fwd+select": 224,
+                  "swa_fwd": 243, "swa_dq": 393, "cmp_dq": 375, "cmp_dkv(+reduce)": 279}
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -142,15 +150,25 @@ def cpu_step(sample_T, steps, warmup):
 
 
 def run_reference(args):
+    """The CPU arm: every step is the oracle's fwd+bwd on a bounded 1024-token sample of one sequence of the workload.
+    All requested steps are run unless they would take longer than about two minutes; the line reports the steps
+    that were really timed."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cb, sec = cpu_step(1024, max(1, min(args.steps, 3)), 1 if args.warmup > 0 else 0)
+    _, sec1 = cpu_step(1024, 1, 0)                       # one untimed-for-the-record step sizes the run
+    budget = 120.0
+    steps = max(1, min(args.steps, int(budget / max(sec1, 1e-3))))
+    warm = max(0, min(args.warmup, int(0.25 * budget / max(sec1, 1e-3))))
+    cb, sec = cpu_step(1024, steps, warm)
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "steps": steps, "warmup": warm, "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "reference_arm": "CPU restatement (oracle) of the reference's naive "
-                       "torch path; each step is a bounded 1024-token sample of the workload"},
+                       "torch path; each step is a bounded 1024-token sample of one sequence of the workload.  Cost per "
+                       "token grows with the sequence length (compressed and selected branches), so tokens/s at 1024 "
+                       "tokens is an UPPER bound for the CPU at the workload's T=8192"},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -204,6 +222,8 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
         "sel_fwd": lambda: L.nsa_sel_swa_fwd(P(q4), P(k4), P(v4), P(idx), 0, None, P(o_slc), P(lse_slc), None, None, None,
                                              None, None, None, None, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"], 0,
                                              scale, S()),
+        "gather_probe": lambda: L.nsa_gather_probe(P(k4), P(v4), P(idx), 0, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"],
+                                                   S()),
         "swa_fwd": lambda: L.nsa_sel_swa_fwd(P(q4), P(k4), P(v4), None, 0, None, None, None, P(o_swa), P(lse_swa), None,
                                              None, None, None, None, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"],
                                              c["window"], scale, S()),
@@ -398,16 +418,34 @@ def run_gpu(args):
     _lib.device_status()
     ms_e2e, _, _ = timed(step_e2e, max(1, min(args.steps, 5)), 1)
     _lib.device_status()
+    h2d_bytes = sum(host[n].numel() * 2 for n in ("q", "k", "v", "do"))
+    d2h_bytes = sum(t.numel() * 2 for t in out_h.values())
 
     tokens = c["B"] * T
-    line = None
+    kern = keys_per = None
     if rank == 0:
-        peaks = read_peaks()
         with torch.no_grad():
             kern, keys_per = per_kernel_breakdown(torch, nsa_b200, mod, q.detach().view(Bl, T, Hq, D),
                                                   k.detach().view(Bl, T, Hkv, D), v.detach().view(Bl, T, Hkv, D),
                                                   do.view(Bl, T, Hq, D))
+    # the main workload's tensors are no longer needed: make room for the secondary workloads
+    del q, k, v, do, host, out_h
+    torch.cuda.empty_cache()
+    secondary = {}
+    sec_steps = max(2, min(args.steps, 5))
+    if world == 1 and not args.no_secondary:
+        secondary["selection_microbench"] = selection_microbench(torch, dev, read_peaks())
+    if not args.no_secondary:
+        secondary["context"] = measure_context(torch, dist, nsa_b200, rank, world, dev, sec_steps, 2, single_gpu_base=True)
+        secondary["decode"] = measure_decode(torch, dist, nsa_b200, rank, world, dev, max(sec_steps, 5), 3)
+
+    if rank == 0:
+        peaks = read_peaks()
         fm_nom = flop_model(c["B"], T, Hq, Hkv, D, c["block"], c["stride"], c["sel_block"], c["n_sel"], c["window"])
+        # the selection follows the reference's unmasked scoring, so about half of a token's 16 blocks lie in its future
+        # and are skipped by every kernel: the FLOPs that count are those of the keys actually visited
+        fm_vis = flop_model(c["B"], T, Hq, Hkv, D, c["block"], c["stride"], c["sel_block"], c["n_sel"], c["window"],
+                            nsel_pairs=keys_per)
         fm_loc = flop_model(Bl, T, Hq, Hkv, D, c["block"], c["stride"], c["sel_block"], c["n_sel"], c["window"],
                             nsel_pairs=keys_per)
         # algorithmic flops per kernel launch (per rank): forward 4D per (row,key); the backward's 10D per (row,key)
@@ -418,29 +456,40 @@ def run_gpu(args):
             "sel+swa_dkv(+reverse index)": 1.5 * (fm_loc["slc"] + fm_loc["swa"]), "cmp_dkv(+reduce)": 1.5 * fm_loc["cmp"],
             "compress_fwd(one of k,v)": fm_loc["comp"] / 2, "compress_bwd(one of k,v)": fm_loc["comp"],
         }
-        # DRAM traffic per launch of the kernels that can dominate: dram__bytes_read + write from one ncu capture of
-        # the B=1 case (profiles/ncu_sections_tcgen05_and_sel_kernels_B1_T8192.md), which grows in proportion to the
-        # number of sequences (every sequence's K/V stays in L2, q/dO/o/dq are streamed once)
-        ncu_mb_per_seq = {"sel_fwd": 237, "sel_dq": 376, "sel+swa_dkv(+reverse index)": 875, "cmp_attn_fwd+select": 224,
-                          "swa_fwd": 243, "swa_dq": 393, "cmp_dq": 375, "cmp_dkv(+reduce)": 279}
+        # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels that can dominate, from
+        # one ncu capture of the B=1 slice of this workload (`--profile-case`), in MB per sequence; traffic grows in
+        # proportion to the number of sequences (every sequence's K/V stays in L2, q/dO/o/dq are streamed once).
+        # NCU_TRAFFIC_COMMIT names the build the capture was taken from: a kernel changed since then has a stale entry.
         dom = max((n for n in kern if n in kflops), key=lambda n: kern[n])
+        # kernels timed alone (three launches back to back): the burst bf16 peak is their denominator
+        peak = peaks["tf_burst"]
+        kroof = {}
+        for n in kflops:
+            ach = kflops[n] / (kern[n] * 1e-3) / 1e12
+            kroof[n] = {"ms": round(kern[n], 3), "tflops": round(ach, 1), "frac_of_burst_peak": round(ach / peak, 4)}
+        # selected attention: the L2 -> SM gather of 32 KB (K and V block) per visited (token, kv head, block), used by
+        # 16 query rows only, against the rate of the same gather with no arithmetic behind it (nsa_gather_probe)
+        visits = keys_per * Bl * Hkv / c["sel_block"]
+        gbytes = visits * 2 * c["sel_block"] * D * 2
+        for n in ("sel_fwd", "sel_dq"):
+            kroof[n].update({"pipe": "mma.sync (peak 574 TFLOP/s measured for m16n8k16 bf16)",
+                             "frac_of_mma_sync_peak": round(kroof[n]["tflops"] / 574.0, 4),
+                             "gather_bytes": gbytes, "gather_tbs": round(gbytes / (kern[n] * 1e-3) / 1e12, 2),
+                             "gather_ceiling_tbs": round(gbytes / (kern["gather_probe"] * 1e-3) / 1e12, 2),
+                             "frac_of_gather_ceiling": round(kern["gather_probe"] / kern[n], 4)})
         achieved = kflops[dom] / (kern[dom] * 1e-3) / 1e12
-        peak = peaks["tf_sustained"]
         roof = {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 2), "peak": peak, "unit": "TFLOP/s",
-                "frac": round(achieved / peak, 4), "peak_source": peaks["source"] + " (sustained bf16 GEMM)",
-                "traffic": (ncu_mb_per_seq[dom] * 1e6 * Bl) if dom in ncu_mb_per_seq else None,
-                "traffic_source": "ncu capture at B=1 x sequences per rank", "ms_per_launch": round(kern[dom], 3),
-                "algorithmic_flops_per_launch": kflops[dom]}
+                "frac": round(achieved / peak, 4), "peak_source": peaks["source"] + " (burst bf16 GEMM: the kernel is timed alone)",
+                "frac_of_sustained_peak": round(achieved / peaks["tf_sustained"], 4),
+                "traffic": (NCU_MB_PER_SEQ[dom] * 1e6 * Bl) if dom in NCU_MB_PER_SEQ else None,
+                "traffic_source": "ncu capture at B=1 (build %s) x sequences per rank" % NCU_TRAFFIC_COMMIT,
+                "ms_per_launch": round(kern[dom], 3), "algorithmic_flops_per_launch": kflops[dom]}
         if dom in ("sel_fwd", "sel_dq"):
-            # these kernels run mma.sync (16 query rows per KV head cannot fill a tcgen05 tile); 574 TFLOP/s is the
-            # m16n8k16 bf16 rate measured on this GPU type with every scheduler issuing back to back
-            roof["pipe"] = "mma.sync"
-            roof["frac_of_mma_sync_peak"] = round(achieved / 574.0, 4)
+            roof.update({k_: v_ for k_, v_ in kroof[dom].items() if k_.startswith(("pipe", "frac_of_", "gather"))})
         cb = None
         if world == 1 and not args.no_cpu:
             cb, _ = cpu_step(1024, 1, 0)
-        h2d = sum(host[n].numel() * 2 for n in ("q", "k", "v", "do"))
-        d2h = sum(t.numel() * 2 for t in out_h.values())
+        tf_vis = fm_vis["total"] / (ms_step * 1e-3) / 1e12
         line = {
             "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -448,14 +497,20 @@ def run_gpu(args):
             "config": {"workload": WORKLOAD, "global_batch": c["B"], "seq_len": T, "parallelism": "batch-sharded x%d" % world,
                        "l2": "inputs larger than L2 (q and dO are 1.07 GB each at N=1)",
                        "selection": "indices produced by the fused top-16 of the step itself (oracle-style scoring)"},
-            "tflops_algorithmic": fm_nom["total"] / (ms_step * 1e-3) / 1e12,
-            "tflops_frac_of_sustained_peak": fm_nom["total"] / (ms_step * 1e-3) / 1e12 / world / peaks["tf_sustained"],
+            # FLOPs of the keys actually visited (see above); the nominal figure (16 visited blocks per token) is kept
+            # beside it under its own name
+            "tflops_algorithmic": tf_vis,
+            "tflops_frac_of_sustained_peak": tf_vis / world / peaks["tf_sustained"],
+            "tflops_frac_of_burst_peak": tf_vis / world / peaks["tf_burst"],
+            "tflops_nominal_selection": fm_nom["total"] / (ms_step * 1e-3) / 1e12,
+            "flops_visited_per_step": fm_vis["total"], "flops_nominal_per_step": fm_nom["total"],
             "host_affinity": numa,
-            "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
-                    "d2h_bytes_per_step": d2h * world, "ms_per_step": ms_e2e},
+            "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes * world,
+                    "d2h_bytes_per_step": d2h_bytes * world, "ms_per_step": ms_e2e,
+                    "host_gbs_aggregate": round((h2d_bytes + d2h_bytes) * world / (ms_e2e * 1e-3) / 1e9, 1)},
             "gpu_launches": int(launches[1] - launches[0]),
-            "roofline": roof, "kernels_ms": {n: round(v, 3) for n, v in kern.items()},
-            "selected_keys_per_seq_kvhead": keys_per, "clocks": clocks, "cpu_baseline": cb,
+            "roofline": roof, "kernels_ms": {n: round(v_, 3) for n, v_ in kern.items()}, "kernel_rooflines": kroof,
+            "selected_keys_per_seq_kvhead": keys_per, "clocks": clocks, "cpu_baseline": cb, "secondary": secondary,
         }
         print(json.dumps(line))
     if world > 1:
@@ -463,57 +518,18 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
-def run_context(args):
-    """BASELINE configs[3]: one sequence of 65536 tokens, fwd+bwd, context-sharded over the ranks (zig-zag chunks,
-    NCCL all-gather of K/V, reduce-scatter of dK/dV, all-reduce of the weight gradients).  N=1 is the scaling base."""
-    import torch
-    import torch.distributed as dist
-    import nsa_b200
-    from nsa_b200 import _lib
-    from nsa_b200.context_parallel import context_parallel_forward
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    c = dict(CFG, B=1, T=65536, seed=3)
-    T, Hq, Hkv, D = c["T"], c["Hq"], c["Hkv"], c["D"]
-    Tl = T // world
-    gen = torch.Generator().manual_seed(c["seed"] * 1000 + rank)
-    q, k, v, do = (torch.randn(1, Tl, h, D, generator=gen).to(dev, torch.bfloat16) for h in (Hq, Hkv, Hkv, Hq))
-    wgen = torch.Generator().manual_seed(c["seed"])
-    mod = nsa_b200.NSAAttention(D, True, None, 0.0, device=dev, dtype=torch.bfloat16)
-    with torch.no_grad():
-        for p in mod.parameters():
-            p.copy_(torch.randn(p.shape, generator=wgen) * 0.02)
-    params = list(mod.parameters())
-    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
-    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
-
-    def step():
-        for t in [q, k, v] + params:
-            t.grad = None
-        if world == 1:
-            o = mod(q.view(T, Hq, D), k.view(T, Hkv, D), v.view(T, Hkv, D), cu, T)
-            o.backward(do.view(T, Hq, D))
-        else:
-            o = context_parallel_forward(mod, q, k, v, None, zigzag=True)
-            o.backward(do)
-            flat = torch.cat([p.grad.reshape(-1) for p in params])
-            dist.all_reduce(flat)
-
-    for _ in range(args.warmup):
-        step()
+def _event_time(torch, dist, fn, steps, warmup, world, dev):
+    """CUDA-event time of `steps` calls after `warmup`, barrier + synchronize on both sides, max over ranks; ms per call."""
+    for _ in range(warmup):
+        fn()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        step()
+    for _ in range(steps):
+        fn()
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -522,41 +538,160 @@ def run_context(args):
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_step = float(ms.item()) / args.steps
+    return float(ms.item()) / steps
+
+
+def config1_indices(torch, B, T, H, S, BS, gen, device):
+    """BASELINE.json configs[1]: per (b, t, kv head) min(S, t//BS+1) distinct blocks drawn uniformly from the causally
+    valid ones, always with block 0 and the query's local block; unused slots are -1."""
+    t = torch.arange(T, device=device)
+    nblk = (t // BS + 1).view(1, T, 1, 1)
+    NB = T // BS
+    r = torch.rand(B, T, H, NB, generator=gen, device=device)
+    blk = torch.arange(NB, device=device).view(1, 1, 1, NB)
+    r = torch.where(blk < nblk, r, torch.full_like(r, -1.0))
+    r = torch.where((blk == 0) | (blk == nblk - 1), torch.full_like(r, 2.0), r)
+    top = torch.topk(r, S, dim=-1)
+    return torch.where(top.values >= 0, top.indices, torch.full_like(top.indices, -1)).to(torch.int32)
+
+
+def selection_microbench(torch, dev, peaks):
+    """BASELINE.json configs[1]: the selected-attention forward alone, B=4 T=8192 Hq=64 Hkv=4 D=128 bf16, top-16 of
+    64-key blocks, all 16 blocks causally valid (window 0), seed 1; once with a warm L2 and once with a 512 MB write
+    between launches.  Also the gather ceiling (nsa_gather_probe) on the same indices."""
+    from nsa_b200 import _lib
+    L, P, S = _lib.lib(), _lib.ptr, _lib.stream
+    B, T, Hq, Hkv, D, n, BS = 4, 8192, 64, 4, 128, 16, 64
+    gen = torch.Generator(device=dev).manual_seed(1)
+    q = torch.randn(B, T, Hq, D, generator=gen, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(B, T, Hkv, D, generator=gen, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(B, T, Hkv, D, generator=gen, device=dev, dtype=torch.bfloat16)
+    idx = config1_indices(torch, B, T, Hkv, n, BS, gen, dev)
+    o = torch.empty_like(q)
+    lse = torch.empty(B, T, Hq, dtype=torch.float32, device=dev)
+    scale = D ** -0.5
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def fwd():
+        _lib.check(L.nsa_sel_swa_fwd(P(q), P(k), P(v), P(idx), 0, None, P(o), P(lse), None, None, None, None, None, None,
+                                     None, B, T, Hq, Hkv, D, n, BS, 0, scale, S()), "nsa_sel_swa_fwd")
+
+    def probe():
+        _lib.check(L.nsa_gather_probe(P(k), P(v), P(idx), 0, B, T, Hq, Hkv, D, n, BS, S()), "nsa_gather_probe")
+
+    def timed(fn, reps, flushed):
+        tot = 0.0
+        for _ in range(reps):
+            if flushed:
+                flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        return tot / reps
+
+    for _ in range(3):
+        fwd()
+        probe()
+    torch.cuda.synchronize()
+    ms_warm, ms_cold = timed(fwd, 10, False), timed(fwd, 5, True)
+    ms_probe = timed(probe, 5, False)
     _lib.device_status()
-    if rank == 0:
-        fm = flop_model(1, T, Hq, Hkv, D, c["block"], c["stride"], c["sel_block"], c["n_sel"], c["window"])
-        print(json.dumps({
-            "metric": METRIC, "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "configs[3]: NSAAttention fwd+bwd bf16, B=1 T=65536 Hq=64 Hkv=4 D=128, context-sharded "
-                                   "(zig-zag chunks, NCCL all-gather of K/V, reduce-scatter of dK/dV)",
-                       "parallelism": "context-sharded x%d" % world},
-            "tflops_algorithmic": fm["total"] / (ms_step * 1e-3) / 1e12}))
-    if world > 1:
+    visits = int(((idx >= 0) & (idx.long() * BS <= torch.arange(T, device=dev).view(1, T, 1, 1))).sum().item())
+    flops = 4.0 * D * (Hq // Hkv) * BS * visits
+    gbytes = visits * 2.0 * BS * D * 2
+    return {"workload": "configs[1]: selection_attn forward, B=4 T=8192 Hq=64 Hkv=4 D=128 bf16, top-16 of 64-key blocks, "
+                        "indices uniform over causally valid blocks incl. block 0 and the local block, window 0, seed 1",
+            "ms_warm_l2": round(ms_warm, 3), "ms_l2_flushed": round(ms_cold, 3),
+            "tokens_per_s": B * T / (ms_warm * 1e-3),
+            "visited_blocks_per_token_kvhead": visits / (B * T * Hkv),
+            "tflops": round(flops / (ms_warm * 1e-3) / 1e12, 1),
+            "frac_of_burst_peak": round(flops / (ms_warm * 1e-3) / 1e12 / peaks["tf_burst"], 4),
+            "frac_of_mma_sync_peak": round(flops / (ms_warm * 1e-3) / 1e12 / 574.0, 4),
+            "gather_bytes": gbytes, "gather_tbs": round(gbytes / (ms_warm * 1e-3) / 1e12, 2),
+            "gather_ceiling_ms": round(ms_probe, 3), "gather_ceiling_tbs": round(gbytes / (ms_probe * 1e-3) / 1e12, 2),
+            "frac_of_gather_ceiling": round(ms_probe / ms_warm, 4)}
+
+
+def measure_context(torch, dist, nsa_b200, rank, world, dev, steps, warmup, single_gpu_base=False):
+    """BASELINE configs[3]: one sequence of 65536 tokens, fwd+bwd, context-sharded over the ranks (zig-zag query chunks;
+    see nsa_b200/context_parallel.py for what crosses NVLink).  With `single_gpu_base` and more than one rank, rank 0
+    also times the unsharded step alone so the record carries its own scaling efficiency."""
+    from nsa_b200 import _lib
+    from nsa_b200.context_parallel import context_parallel_forward
+    c = dict(CFG, B=1, T=65536, seed=3)
+    T, Hq, Hkv, D = c["T"], c["Hq"], c["Hkv"], c["D"]
+    Tl = T // world
+    gen = torch.Generator(device=dev).manual_seed(c["seed"] * 1000 + rank)
+    q, k, v, do = (torch.randn(1, Tl, h, D, generator=gen, device=dev, dtype=torch.bfloat16) for h in (Hq, Hkv, Hkv, Hq))
+    wgen = torch.Generator().manual_seed(c["seed"])
+    mod = nsa_b200.NSAAttention(D, True, None, 0.0, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.copy_(torch.randn(p.shape, generator=wgen) * 0.02)
+    params = list(mod.parameters())
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+
+    def step_single(qq, kk, vv, dd):
+        Tn = qq.shape[1]
+        cu = torch.tensor([0, Tn], dtype=torch.int32, device=dev)
+        for t in [qq, kk, vv] + params:
+            t.grad = None
+        o = mod(qq.view(Tn, Hq, D), kk.view(Tn, Hkv, D), vv.view(Tn, Hkv, D), cu, Tn)
+        o.backward(dd.view(Tn, Hq, D))
+
+    def step():
+        if world == 1:
+            step_single(q, k, v, do)
+            return
+        for t in [q, k, v] + params:
+            t.grad = None
+        o = context_parallel_forward(mod, q, k, v, None, zigzag=True)
+        o.backward(do)
+        flat = torch.cat([p.grad.reshape(-1) for p in params])
+        dist.all_reduce(flat)
+
+    ms_step = _event_time(torch, dist, step, steps, warmup, world, dev)
+    _lib.device_status()
+    out = {"workload": "configs[3]: NSAAttention fwd+bwd bf16, B=1 T=65536 Hq=64 Hkv=4 D=128, context-sharded "
+                       "(zig-zag query chunks) x%d" % world,
+           "n_gpus": world, "ms_per_step": ms_step, "tokens_per_s": T / (ms_step * 1e-3), "steps": steps}
+    fm = flop_model(1, T, Hq, Hkv, D, c["block"], c["stride"], c["sel_block"], c["n_sel"], c["window"])
+    out["tflops_nominal_selection"] = fm["total"] / (ms_step * 1e-3) / 1e12
+    if world > 1 and single_gpu_base:
+        base = torch.zeros(1, device=dev)
+        del q, k, v, do
+        torch.cuda.empty_cache()
+        if rank == 0:
+            g2 = torch.Generator(device=dev).manual_seed(c["seed"] * 1000)
+            qf, kf, vf, df = (torch.randn(1, T, h, D, generator=g2, device=dev, dtype=torch.bfloat16)
+                              for h in (Hq, Hkv, Hkv, Hq))
+            qf.requires_grad_(True), kf.requires_grad_(True), vf.requires_grad_(True)
+            base[0] = _event_time(torch, dist, lambda: step_single(qf, kf, vf, df), 2, 1, 1, dev)
+            del qf, kf, vf, df
         dist.barrier()
-        dist.destroy_process_group()
+        dist.broadcast(base, 0)
+        out["single_gpu_ms_per_step_same_process"] = float(base.item())
+        out["scaling_efficiency_vs_single_gpu"] = float(base.item()) / (ms_step * world)
+    torch.cuda.empty_cache()
+    return out
 
 
-def run_decode(args):
+def decode_lengths():
+    import torch
+    return torch.randint(4096, 32769, (128,), generator=torch.Generator().manual_seed(4)).tolist()
+
+
+def measure_decode(torch, dist, nsa_b200, rank, world, dev, steps, warmup):
     """BASELINE configs[4]: 128 sequences with KV lengths uniform in [4096, 32768] (seed 4), one new query token each;
     sequences are assigned to the ranks by longest-processing-time bin packing (work ~ L); no collective."""
-    import torch
-    import torch.distributed as dist
-    import nsa_b200
     from nsa_b200 import _lib
     from nsa_b200.decode import compress_cache, nsa_decode
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     c = CFG
     Hq, Hkv, D = c["Hq"], c["Hkv"], c["D"]
-    lens = torch.randint(4096, 32769, (128,), generator=torch.Generator().manual_seed(4)).tolist()
+    lens = decode_lengths()
     bins = [[] for _ in range(world)]
     load = [0] * world
     for i in sorted(range(128), key=lambda i: -lens[i]):
@@ -567,56 +702,75 @@ def run_decode(args):
     cu = [0]
     for n in mine:
         cu.append(cu[-1] + n)
-    gen = torch.Generator().manual_seed(4000 + rank)
-    q = torch.randn(len(mine), Hq, D, generator=gen).to(dev, torch.bfloat16)
-    k = torch.randn(cu[-1], Hkv, D, generator=gen).to(dev, torch.bfloat16)
-    v = torch.randn(cu[-1], Hkv, D, generator=gen).to(dev, torch.bfloat16)
+    gen = torch.Generator(device=dev).manual_seed(4000 + rank)
+    q = torch.randn(len(mine), Hq, D, generator=gen, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(cu[-1], Hkv, D, generator=gen, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(cu[-1], Hkv, D, generator=gen, device=dev, dtype=torch.bfloat16)
     mod = nsa_b200.NSAAttention(D, True, None, 0.0, device=dev, dtype=torch.bfloat16)
     with torch.no_grad():
         for p in mod.parameters():
             p.copy_(torch.randn(p.shape, generator=torch.Generator().manual_seed(4)) * 0.02)
-
-    def timed(fn):
-        for _ in range(args.warmup):
-            fn()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item()) / args.steps
-
-    with torch.no_grad():
-        ms_stateless = timed(lambda: nsa_decode(mod, q, k, v, cu))
+        ms_stateless = _event_time(torch, dist, lambda: nsa_decode(mod, q, k, v, cu), steps, warmup, world, dev)
         cache = compress_cache(mod, k, v, cu)
-        ms_cached = timed(lambda: nsa_decode(mod, q, k, v, cu, cache=cache))
+        ms_cached = _event_time(torch, dist, lambda: nsa_decode(mod, q, k, v, cu, cache=cache), steps, warmup, world, dev)
     _lib.device_status()
+    peaks = read_peaks()
+    # bytes a step must read: stateless = all of K and V once (they are re-compressed); cached = the compressed cache,
+    # the selected blocks and the window of every sequence
+    kv_bytes = sum(lens) * Hkv * D * 2 * 2
+    n_c = sum((L - c["block"]) // c["stride"] + 1 for L in lens)
+    cached_bytes = (n_c + 128 * (c["n_sel"] * c["sel_block"] + c["window"])) * Hkv * D * 2 * 2
+    out = {"workload": "configs[4]: varlen decode, 128 sequences, KV length U[4096,32768] seed 4, Hq=64 Hkv=4 D=128, "
+                       "sequence-sharded x%d (LPT)" % world,
+           "n_gpus": world, "sum_kv_len": sum(lens), "steps": steps,
+           "stateless": {"ms_per_step": ms_stateless, "tokens_per_s": 128 / (ms_stateless * 1e-3),
+                         "algorithmic_bytes": kv_bytes,
+                         "hbm_gbs_per_gpu": round(kv_bytes / (ms_stateless * 1e-3) / 1e9 / world, 1),
+                         "frac_of_hbm_peak": round(kv_bytes / (ms_stateless * 1e-3) / 1e9 / world / peaks["hbm_gbs"], 4)},
+           "with_compressed_cache": {"ms_per_step": ms_cached, "tokens_per_s": 128 / (ms_cached * 1e-3),
+                                     "algorithmic_bytes": cached_bytes,
+                                     "hbm_gbs_per_gpu": round(cached_bytes / (ms_cached * 1e-3) / 1e9 / world, 1),
+                                     "frac_of_hbm_peak": round(cached_bytes / (ms_cached * 1e-3) / 1e9 / world / peaks["hbm_gbs"], 4)}}
+    del q, k, v, cache
+    torch.cuda.empty_cache()
+    return out
+
+
+def _secondary_only(args, which):
+    """`--workload context|decode`: the secondary workload alone, as its own JSON line."""
+    import torch
+    import torch.distributed as dist
+    import nsa_b200
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if which == "context":
+        r = measure_context(torch, dist, nsa_b200, rank, world, dev, args.steps, args.warmup, single_gpu_base=args.base)
+        value, ms, metric = r["tokens_per_s"], r["ms_per_step"], METRIC
+    else:
+        r = measure_decode(torch, dist, nsa_b200, rank, world, dev, args.steps, args.warmup)
+        value, ms = r["with_compressed_cache"]["tokens_per_s"], r["with_compressed_cache"]["ms_per_step"]
+        metric = "NSA decode tokens/s (one new token per sequence, compressed cache kept)"
     if rank == 0:
-        peaks = read_peaks()
-        kv_bytes = sum(lens) * Hkv * D * 2 * 2
-        print(json.dumps({
-            "metric": "NSA decode tokens/s (one new token per sequence)", "value": 128 / (ms_stateless * 1e-3),
-            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_stateless,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "configs[4]: varlen decode, 128 sequences, KV length U[4096,32768] seed 4, Hq=64 Hkv=4 "
-                                   "D=128; stateless (re-compresses the whole cache every step)",
-                       "parallelism": "sequence-sharded x%d (LPT)" % world, "sum_kv_len": sum(lens)},
-            "with_compressed_cache": {"ms_per_step": ms_cached, "tokens_per_s": 128 / (ms_cached * 1e-3)},
-            "roofline": {"bound": "hbm", "achieved": round(kv_bytes / (ms_stateless * 1e-3) / 1e9 / world, 1),
-                         "peak": peaks["hbm_gbs"], "unit": "GB/s per GPU",
-                         "frac": round(kv_bytes / (ms_stateless * 1e-3) / 1e9 / world / peaks["hbm_gbs"], 4),
-                         "traffic": None, "algorithmic_bytes": kv_bytes}}))
+        print(json.dumps({"metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {"workload": r["workload"]},
+                          "detail": r}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_context(args):
+    _secondary_only(args, "context")
+
+
+def run_decode(args):
+    _secondary_only(args, "decode")
 
 
 def run_profile_case():
@@ -644,6 +798,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (configs[1], [3], [4])")
+    ap.add_argument("--base", action="store_true", help="--workload context with N > 1: also time the unsharded step on rank 0")
     ap.add_argument("--workload", default="module", choices=["module", "context", "decode"],
                     help="module: configs[2], batch-sharded (default).  context: configs[3], B=1 T=65536 context-sharded")
     ap.add_argument("--profile-case", action="store_true",

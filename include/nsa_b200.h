@@ -81,6 +81,15 @@ int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, flo
                      float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride,
                      int causal, float scale, int n_sel, int pool_k, int pool_s, int pool_p, void* stream);
 int nsa_pool_out_len(int n, int pool_k, int pool_s, int pool_p);
+/* nsa_cmp_attn_fwd_sharded with the module's gate projection fused in: while the query tile is resident the kernel also
+ * computes g_x[r] = q[r,:] . gate_w[x,:] + gate_b[x] for x = 0,1,2 = selected, window, compressed (gate_w [3,D] bf16,
+ * gate_b [3] bf16 or NULL, no activation) and writes the three gates to g_slc, g_swa, g_cmp [B,Tq,Hq] bf16.
+ * Replaces, in addition, self.gating = nn.Linear(head_dim, 3) applied at nsa/nsa.py:117.  Tq = T, q0 = 0 for an
+ * unsharded call. */
+int nsa_cmp_attn_fwd_gated(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
+                           float* sel_scores, const void* gate_w, const void* gate_b, void* g_slc, void* g_swa, void* g_cmp,
+                           int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal, float scale,
+                           int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream);
 /* Replaces _attention.backward (nsa/triton_attention.py:479-546).  dout [B,T,Hq,D]; delta [B,T,Hq] fp32 =
  * rowsum(o*dout) (times gate if gate != NULL); gate [B,T,Hq] or NULL scales dout per row.
  * dq [B,T,Hq,D] (added to when accumulate_dq); dck,dcv [B,Tc,Hk,D]. */
@@ -110,6 +119,13 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
                     int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
                     int D, int S, int BS, int window, float scale, void* stream);
 size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS);
+
+/* Measurement aid, no counterpart in the reference: the K/V block gather of nsa_sel_swa_fwd's selected branch (same
+ * items, same order, same TMA boxes of [BS keys x D]) with no arithmetic behind it, every SM keeping all of its shared
+ * memory in flight.  visited blocks x 2 x BS x D x 2 bytes divided by its run time is the L2 -> SM gather ceiling that
+ * the benchmark reports beside the selected-attention kernels.  Needs BS = 64 and S <= 32. */
+int nsa_gather_probe(const void* k, const void* v, const void* idx, int idx64, int B, int T, int Hq, int Hkv, int D, int S,
+                     int BS, void* stream);
 
 /* ---- query shards (context parallelism) -------------------------------------------------------------
  * No counterpart in the reference (it is single-GPU: neither its modules nor its tests hold distributed code).  The four

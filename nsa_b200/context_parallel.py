@@ -55,6 +55,7 @@ class _GatherTokens(torch.autograd.Function):
             out = torch.empty_like(blocks[rank])
             dist.reduce_scatter(out, [b.contiguous() for b in blocks], group=group)
             return out, None, None
+        g = g.clone()          # the incoming gradient may be shared with other consumers: reduce a private copy
         dist.all_reduce(g, group=group)
         return torch.cat([g[:, cid * cl:(cid + 1) * cl] for cid in layout[rank]], dim=1), None, None
 

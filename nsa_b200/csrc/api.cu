@@ -87,7 +87,7 @@ int nsa_device_status(void) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(1000 + (int)e, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
   int worst = 0, v = 0;
-  int (*fns[])(int*) = {sel_status, sel_block_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_tc_status, dense_dq_tc_status};
+  int (*fns[])(int*) = {sel_status, sel_block_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_tc_status, dense_dq_tc_status, gather_probe_status, dense_tc2_status};
   for (auto f : fns) {
     v = 0;
     const int rc = f(&v);
@@ -173,9 +173,15 @@ int nsa_compress_bwd_noalloc(const void* x, const void* w, const void* dy, void*
 }
 
 // ---- compressed attention ---------------------------------------------------------------------------
+struct GateArgs {   // optional gate projection fused into the compressed-attention forward
+  const void *w, *b;
+  void* g[3];
+};
+
 static int cmp_attn_fwd_impl(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
                      float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
-                     float scale, int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream) {
+                     float scale, int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream,
+                     const GateArgs* gate = nullptr) {
   const bool sharded = (Tq != T) || (q0 != 0);
   if (Tq <= 0 || q0 < 0 || q0 + Tq > T) return fail(-12, "%s: query shard [%d, %d) is outside the sequence of %d tokens", "nsa_cmp_attn_fwd", q0, q0 + Tq, T);
   (void)sharded;
@@ -196,9 +202,18 @@ static int cmp_attn_fwd_impl(const void* q, const void* ck, const void* cv, void
     a.n_pool = nsa_pool_out_len(Tc, pool_k, pool_s, pool_p);
     a.sel_idx = sel_idx; a.sel_scores = sel_scores;
   }
-  if (dense_fwd_tc_supported(a, D)) return launch_dense_fwd_tc(a, (cudaStream_t)stream);
+  if (dense_fwd_tc_supported(a, D)) {
+    if (gate) {
+      a.gate_w = (const bf16*)gate->w; a.gate_b = (const bf16*)gate->b;
+      for (int i = 0; i < 3; ++i) a.g_out[i] = (bf16*)gate->g[i];
+    }
+    return launch_dense_fwd2_tc(a, (cudaStream_t)stream);
+  }
   if (sharded) return fail(-11, "query shards need head_dim 128 and the default pooling geometry");
-  return launch_dense_fwd(a, D, (cudaStream_t)stream);
+  rc = launch_dense_fwd(a, D, (cudaStream_t)stream);
+  if (rc || !gate) return rc;
+  return launch_gate_fwd((const bf16*)q, (const bf16*)gate->w, (const bf16*)gate->b, (bf16*)gate->g[0], (bf16*)gate->g[1],
+                         (bf16*)gate->g[2], (long long)B * Tq * Hq, D, (cudaStream_t)stream);
 }
 
 int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
@@ -211,6 +226,15 @@ int nsa_cmp_attn_fwd_sharded(const void* q, const void* ck, const void* cv, void
                      float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
                      float scale, int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream) {
   return cmp_attn_fwd_impl(q, ck, cv, o, lse, sel_idx, sel_scores, B, T, Tc, Hq, Hk, D, block, stride, causal, scale, n_sel, pool_k, pool_s, pool_p, Tq, q0, stream);
+}
+
+int nsa_cmp_attn_fwd_gated(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
+                           float* sel_scores, const void* gate_w, const void* gate_b, void* g_slc, void* g_swa, void* g_cmp,
+                           int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal, float scale,
+                           int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream) {
+  if (!gate_w || !g_slc || !g_swa || !g_cmp) return fail(-1, "nsa_cmp_attn_fwd_gated: null gate weight or gate output");
+  const GateArgs g = {gate_w, gate_b, {g_slc, g_swa, g_cmp}};
+  return cmp_attn_fwd_impl(q, ck, cv, o, lse, sel_idx, sel_scores, B, T, Tc, Hq, Hk, D, block, stride, causal, scale, n_sel, pool_k, pool_s, pool_p, Tq, q0, stream, &g);
 }
 
 size_t nsa_cmp_attn_bwd_workspace_bytes(int B, int T, int Tc, int Hk, int D) {
@@ -311,7 +335,16 @@ static int sel_swa_fwd_impl(const void* q, const void* k, const void* v, const v
     a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.o = (bf16*)o_swa; a.lse = lse_swa;
     a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
     if (!dense_fwd_tc_supported(a, D) && sharded) return fail(-11, "query shards need head_dim 128");
-    rc = dense_fwd_tc_supported(a, D) ? launch_dense_fwd_tc(a, s) : launch_dense_fwd(a, D, s);
+    if (dense_fwd_tc_supported(a, D)) {
+      if (o) {   // the gated sum of the branches is written by the window kernel's epilogue
+        a.comb_o = (bf16*)o; a.comb_slc = (const bf16*)o_slc; a.comb_cmp = (const bf16*)o_cmp;
+        a.comb_g[0] = (const bf16*)g_slc; a.comb_g[1] = (const bf16*)g_swa; a.comb_g[2] = (const bf16*)g_cmp;
+        o = nullptr;
+      }
+      rc = launch_dense_fwd2_tc(a, s);
+    } else {
+      rc = launch_dense_fwd(a, D, s);
+    }
     if (rc) return rc;
   }
   if (o) {
@@ -432,6 +465,17 @@ int nsa_sel_swa_bwd_sharded(const void* q, const void* k, const void* v, const v
                     int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
                     int D, int S, int BS, int window, float scale, int Tq, int q0, void* stream) {
   return sel_swa_bwd_impl(q, k, v, idx, idx64, counts, dout_slc, lse_slc, delta_slc, gate_slc, dout_swa, lse_swa, delta_swa, gate_swa, dq, accumulate_dq, dk, dv, ws, ws_bytes, B, T, Hq, Hkv, D, S, BS, window, scale, Tq, q0, stream);
+}
+
+int nsa_gather_probe(const void* k, const void* v, const void* idx, int idx64, int B, int T, int Hq, int Hkv, int D, int S,
+                     int BS, void* stream) {
+  if (!k || !v || !idx) return fail(-1, "nsa_gather_probe: null pointer");
+  int rc = check_attn_shape("nsa_gather_probe", B, T, Hq, Hkv, D);
+  if (rc) return rc;
+  SelArgs a = {};
+  a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64;
+  a.B = B; a.T = T; a.Tq = T; a.q0 = 0; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS;
+  return launch_gather_probe(a, D, (cudaStream_t)stream);
 }
 
 // ---- decode ---------------------------------------------------------------------------------------------

@@ -36,6 +36,9 @@ int sel_status(int* out);
 bool sel_block_supported(const SelArgs& a, int D);
 int launch_sel_block(const SelArgs& a, int D, bool bwd, cudaStream_t s);
 int sel_block_status(int* out);
+// the same gather with nothing behind it (gather_probe.cu): the bandwidth ceiling quoted for these kernels
+int launch_gather_probe(const SelArgs& a, int D, cudaStream_t s);
+int gather_probe_status(int* out);
 
 // ---- dense query-major attention: sliding window (mode 0) and compressed (mode 1) ---------
 struct DenseArgs {
@@ -61,6 +64,14 @@ struct DenseArgs {
   int* sel_idx;        // [B,T,Hq/16,n_sel] int32
   float* sel_scores;   // optional [B,Hq/16,T,n_pool] fp32 dump of the pooled scores, or null
   int Tq, q0;          // query shard: q-indexed tensors hold Tq rows per batch, row i is sequence position q0+i
+  // optional fused epilogues of the two-tile tcgen05 forward (null = off)
+  const bf16* gate_w;  // mode 1: [3,D] gate projection weight (rows: selected, window, compressed); writes g_out
+  const bf16* gate_b;  // [3] or null
+  bf16* g_out[3];      // [B,Tq,Hq] each
+  bf16* comb_o;        // mode 0: comb_o = comb_g[0]*comb_slc + comb_g[1]*o + comb_g[2]*comb_cmp (null tensor: term dropped)
+  const bf16* comb_slc;
+  const bf16* comb_cmp;
+  const bf16* comb_g[3];
 };
 int launch_dense_fwd(const DenseArgs& a, int D, cudaStream_t s);
 int launch_dense_dq(const DenseArgs& a, int D, cudaStream_t s);
@@ -69,6 +80,9 @@ int dense_status(int* out);
 bool dense_fwd_tc_supported(const DenseArgs& a, int head_dim);
 int launch_dense_fwd_tc(const DenseArgs& a, cudaStream_t s);
 int dense_tc_status(int* out);
+// two query tiles per CTA, P kept in tensor memory (dense_fwd2_tc.cu); same support matrix as dense_fwd_tc_supported
+int launch_dense_fwd2_tc(const DenseArgs& a, cudaStream_t s);
+int dense_tc2_status(int* out);
 int launch_dense_dq_tc(const DenseArgs& a, cudaStream_t s);
 int dense_dq_tc_status(int* out);
 

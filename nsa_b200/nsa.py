@@ -27,8 +27,6 @@ class _NSACore(torch.autograd.Function):
         L, P, S = _lib.lib(), _lib.ptr, _lib.stream
         dev = q.device
         g_slc, g_swa, g_cmp = (torch.empty(B, Tq, Hq, dtype=q.dtype, device=dev) for _ in range(3))
-        _lib.check(L.nsa_gate_fwd(P(q), P(w_gate), P(b_gate), P(g_slc), P(g_swa), P(g_cmp), B * Tq * Hq, D, S()),
-                   "nsa_gate_fwd")
         n_pool = L.nsa_pool_out_len(Tc, pool_k, pool_s, pool_p)
         if n_sel > n_pool:
             raise RuntimeError("selected index k out of range: %d blocks requested, %d exist" % (n_sel, n_pool))
@@ -37,9 +35,11 @@ class _NSACore(torch.autograd.Function):
         lse_cmp, lse_slc = (torch.empty(B, Tq, Hq, dtype=torch.float32, device=dev) for _ in range(2))
         lse_swa = torch.empty_like(lse_slc) if window > 0 else None
         idx = torch.empty(B, Tq, Hkv, n_sel, dtype=torch.int32, device=dev)
-        _lib.check(L.nsa_cmp_attn_fwd_sharded(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, B, T, Tc, Hq, Hkv,
-                                              D, block, stride, 1 if causal else 0, scale, n_sel, pool_k, pool_s, pool_p,
-                                              Tq, q0, S()), "nsa_cmp_attn_fwd")
+        # compressed attention + block selection; the gate projection rides on the resident query tiles
+        _lib.check(L.nsa_cmp_attn_fwd_gated(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, P(w_gate), P(b_gate),
+                                            P(g_slc), P(g_swa), P(g_cmp), B, T, Tc, Hq, Hkv, D, block, stride,
+                                            1 if causal else 0, scale, n_sel, pool_k, pool_s, pool_p, Tq, q0, S()),
+                   "nsa_cmp_attn_fwd_gated")
         _lib.check(L.nsa_sel_swa_fwd_sharded(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(lse_slc), P(o_swa),
                                              P(lse_swa), P(g_slc), P(g_swa), P(o_cmp), P(g_cmp), P(o), B, T, Hq, Hkv, D,
                                              n_sel, sel_block, window, scale, Tq, q0, S()), "nsa_sel_swa_fwd")
