@@ -156,18 +156,21 @@ int nsa_sel_swa_bwd_sharded(const void* q, const void* k, const void* v, const v
 
 /* ---- decode ---------------------------------------------------------------------------------------------
  * No entry point of the reference does this (its module assumes len(q) == len(k), nsa/nsa.py:97); it is the
- * module's forward (nsa/nsa.py:94-135) for ONE new query token per sequence, at position L-1 of a packed
- * K/V cache.  q, o and the scratch o_cmp / o_slc / o_swa [nseq,Hq,D]; k, v [sum L,Hkv,D]; ck, cv
- * [sum Tc,Hkv,D] = the compressed cache (nsa_compress_fwd with the Conv1d length rule); cu_k, cu_c: HOST int32
- * [nseq+1]; gates [nseq,Hq] (NULL = 1); lse fp32 [3,nseq,Hq] and idx int32 [nseq,Hkv,n_sel] receive the
- * branch log-sum-exps and the selected blocks.  Needs head_dim 128, 64-key blocks, stride 16 / block 32.
- * The sequences' kernels (a few CTAs each) are spread over a per-device pool of eight internal non-blocking streams
- * that fork from and join `stream` through events: no host synchronisation, and all work is ordered after what was
- * on `stream` before the call and before what is enqueued on it afterwards. */
+ * module's forward (nsa/nsa.py:94-135) for ONE new query token per sequence, at position L-1 of a packed, ragged
+ * K/V cache, all sequences in ONE kernel launch (one CTA per (sequence, kv head), see csrc/decode.cu).
+ * q, o [nseq,Hq,D]; k, v [total_k,Hkv,D]; ck, cv [total_c,Hkv,D] = the compressed cache (nsa_compress_fwd with the
+ * Conv1d length rule Tc = (L-block)/stride + 1); cu_k, cu_c: DEVICE int32 [nseq+1] cumulative lengths of k/v and of
+ * ck/cv; order: DEVICE int32 [nseq] = the order in which sequences are dealt to the CTAs (pass them longest first for
+ * an even load) or NULL; gates [nseq,Hq] (NULL = 1).  Optional outputs (NULL to skip): the branch outputs o_cmp, o_slc,
+ * o_swa [nseq,Hq,D] and lse fp32 [3,nseq,Hq] (compressed, selected, window); idx int32 [nseq,Hkv,n_sel] receives the
+ * selected blocks.  max_Tc = the largest per-sequence compressed length (host-known; at most 2048, i.e. caches up to
+ * 32 K tokens).  Needs head_dim 128, 16 query heads per KV head, 64-key blocks, stride 16 / block 32.  No host
+ * synchronisation, no internal streams: everything is enqueued on `stream`. */
 int nsa_decode_fwd(const void* q, const void* k, const void* v, const void* ck, const void* cv, const int32_t* cu_k,
-                   const int32_t* cu_c, const void* g_slc, const void* g_swa, const void* g_cmp, void* o, void* o_cmp,
-                   void* o_slc, void* o_swa, float* lse, int32_t* idx, int nseq, int Hq, int Hkv, int D, int block,
-                   int stride, int sel_block, int n_sel, int window, float scale, void* stream);
+                   const int32_t* cu_c, const int32_t* order, const void* g_slc, const void* g_swa, const void* g_cmp, void* o,
+                   void* o_cmp, void* o_slc, void* o_swa, float* lse, int32_t* idx, int nseq, long long total_k,
+                   long long total_c, int max_Tc, int Hq, int Hkv, int D, int block, int stride, int sel_block, int n_sel,
+                   int window, float scale, void* stream);
 
 /* ---- helpers --------------------------------------------------------------------------------------
  * delta[r] = (gate ? gate[r] : 1) * sum_d o[r,d]*dout[r,d] (fp32, NULL to skip) and

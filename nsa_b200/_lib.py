@@ -39,7 +39,7 @@ SIGNATURES = {
     "nsa_sel_swa_bwd_sharded": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I,
                                     F, I, I, P]),
     "nsa_gather_probe": (I, [P, P, P, I, I, I, I, I, I, I, I, P]),
-    "nsa_decode_fwd": (I, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P]),
+    "nsa_decode_fwd": (I, [P] * 17 + [I, L, L, I, I, I, I, I, I, I, I, I, F, P]),
     "nsa_rowdot": (I, [P, P, P, P, P, L, I, P]),
     "nsa_combine": (I, [P, P, P, P, P, P, P, L, I, P]),
     "nsa_gate_fwd": (I, [P, P, P, P, P, P, L, I, P]),

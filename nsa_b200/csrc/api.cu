@@ -5,7 +5,6 @@
 
 #include "../../include/nsa_b200.h"
 #include "kernels.h"
-#include <mutex>
 #include "tmap.h"
 
 namespace nsa {
@@ -53,28 +52,6 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 using namespace nsa;
 
-// A per-device pool of non-blocking streams for nsa_decode_fwd (created on first use, never destroyed).
-constexpr int kDecodeStreams = 8;
-static int decode_streams(cudaStream_t (&out)[kDecodeStreams]) {
-  static std::mutex mu;
-  static cudaStream_t pools[64][kDecodeStreams];
-  static bool made[64] = {};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
-  std::lock_guard<std::mutex> lock(mu);
-  if (!made[dev]) {
-    for (int i = 0; i < kDecodeStreams; ++i) {
-      e = cudaStreamCreateWithFlags(&pools[dev][i], cudaStreamNonBlocking);
-      if (e != cudaSuccess) return (int)e;
-    }
-    made[dev] = true;
-  }
-  for (int i = 0; i < kDecodeStreams; ++i) out[i] = pools[dev][i];
-  return 0;
-}
-
 extern "C" {
 
 int nsa_abi_version(void) { return 1; }
@@ -87,7 +64,7 @@ int nsa_device_status(void) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(1000 + (int)e, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
   int worst = 0, v = 0;
-  int (*fns[])(int*) = {sel_status, sel_block_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_tc_status, dense_dq_tc_status, gather_probe_status, dense_tc2_status};
+  int (*fns[])(int*) = {sel_status, sel_block_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_tc_status, dense_dq_tc_status, gather_probe_status, dense_tc2_status, decode_status};
   for (auto f : fns) {
     v = 0;
     const int rc = f(&v);
@@ -480,65 +457,23 @@ int nsa_gather_probe(const void* k, const void* v, const void* idx, int idx64, i
 
 // ---- decode ---------------------------------------------------------------------------------------------
 int nsa_decode_fwd(const void* q, const void* k, const void* v, const void* ck, const void* cv, const int32_t* cu_k,
-                   const int32_t* cu_c, const void* g_slc, const void* g_swa, const void* g_cmp, void* o, void* o_cmp,
-                   void* o_slc, void* o_swa, float* lse, int32_t* idx, int nseq, int Hq, int Hkv, int D, int block,
-                   int stride, int sel_block, int n_sel, int window, float scale, void* stream) {
-  if (!q || !k || !v || !ck || !cv || !cu_k || !cu_c || !o || !o_cmp || !o_slc || !lse || !idx)
-    return fail(-1, "nsa_decode_fwd: null pointer");
-  if (window > 0 && !o_swa) return fail(-1, "nsa_decode_fwd: o_swa is null");
+                   const int32_t* cu_c, const int32_t* order, const void* g_slc, const void* g_swa, const void* g_cmp, void* o,
+                   void* o_cmp, void* o_slc, void* o_swa, float* lse, int32_t* idx, int nseq, long long total_k,
+                   long long total_c, int max_Tc, int Hq, int Hkv, int D, int block, int stride, int sel_block, int n_sel,
+                   int window, float scale, void* stream) {
+  if (!q || !k || !v || !ck || !cv || !cu_k || !cu_c || !o || !idx) return fail(-1, "nsa_decode_fwd: null pointer");
   if (nseq <= 0) return 0;
-  const int pool_k = sel_block / stride + 1, pool_s = sel_block / stride, pool_p = block / stride - 2;
-  const bf16 *qb = (const bf16*)q, *kb = (const bf16*)k, *vb = (const bf16*)v, *ckb = (const bf16*)ck, *cvb = (const bf16*)cv;
-  const bf16 *gs = (const bf16*)g_slc, *gw = (const bf16*)g_swa, *gc = (const bf16*)g_cmp;
-  // Sequences are independent and each one's kernels are a few CTAs, so they are spread over a small pool of
-  // internal streams that fork from and join the caller's stream through events (no host synchronisation; the pool
-  // is created once per device and holds no device memory).
-  cudaStream_t user = (cudaStream_t)stream;
-  cudaStream_t pool[kDecodeStreams];
-  const int nstream = nseq < kDecodeStreams ? nseq : kDecodeStreams;
-  int rc = decode_streams(pool);
-  if (rc) return fail(1000 + rc, "nsa_decode_fwd: creating the stream pool failed: %s", cudaGetErrorString((cudaError_t)rc));
-  cudaEvent_t fork, join[kDecodeStreams];
-  if (cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) != cudaSuccess) return fail(-40, "nsa_decode_fwd: event creation failed");
-  for (int s = 0; s < nstream; ++s)
-    if (cudaEventCreateWithFlags(&join[s], cudaEventDisableTiming) != cudaSuccess) {
-      for (int u = 0; u < s; ++u) cudaEventDestroy(join[u]);
-      cudaEventDestroy(fork);
-      return fail(-40, "nsa_decode_fwd: event creation failed");
-    }
-  cudaEventRecord(fork, user);
-  for (int s = 0; s < nstream; ++s) cudaStreamWaitEvent(pool[s], fork, 0);
-  int err = 0;
-  for (int i = 0; i < nseq && !err; ++i) {
-    cudaStream_t st = pool[i % nstream];
-    const int L = cu_k[i + 1] - cu_k[i], Tc = cu_c[i + 1] - cu_c[i];
-    if (L <= 0 || Tc <= 0) {
-      err = fail(-13, "nsa_decode_fwd: sequence %d is shorter than one compression block", i);
-      break;
-    }
-    const long long qo = (long long)i * Hq * D, ro = (long long)i * Hq;
-    const bf16* ki = kb + (long long)cu_k[i] * Hkv * D;
-    const bf16* vi = vb + (long long)cu_k[i] * Hkv * D;
-    const bf16* cki = ckb + (long long)cu_c[i] * Hkv * D;
-    const bf16* cvi = cvb + (long long)cu_c[i] * Hkv * D;
-    int32_t* idx_i = idx + (long long)i * Hkv * n_sel;
-    // the newest token (position L-1) is the only query: a one-row query shard of the sequence
-    err = cmp_attn_fwd_impl(qb + qo, cki, cvi, (bf16*)o_cmp + qo, lse + ro, idx_i, nullptr, 1, L, Tc, Hq, Hkv, D, block,
-                            stride, 1, scale, n_sel, pool_k, pool_s, pool_p, 1, L - 1, st);
-    if (err) break;
-    err = sel_swa_fwd_impl(qb + qo, ki, vi, idx_i, 0, nullptr, (bf16*)o_slc + qo, lse + (long long)nseq * Hq + ro,
-                           window > 0 ? (bf16*)o_swa + qo : nullptr, lse + 2ll * nseq * Hq + ro, gs ? gs + ro : nullptr,
-                           gw ? gw + ro : nullptr, (bf16*)o_cmp + qo, gc ? gc + ro : nullptr, (bf16*)o + qo, 1, L, Hq, Hkv,
-                           D, n_sel, sel_block, window, scale, 1, L - 1, st);
-  }
-  // always join, also after an error, so the caller's stream stays ordered after whatever was enqueued
-  for (int s = 0; s < nstream; ++s) {
-    cudaEventRecord(join[s], pool[s]);
-    cudaStreamWaitEvent(user, join[s], 0);
-    cudaEventDestroy(join[s]);   // released when the recorded work has completed
-  }
-  cudaEventDestroy(fork);
-  return err;
+  if (total_k <= 0 || total_c <= 0 || Hq <= 0 || Hkv <= 0) return fail(-1, "nsa_decode_fwd: empty shape");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(ck) || !aligned16(cv) || !aligned16(o))
+    return fail(-5, "nsa_decode_fwd: pointers must be 16-byte aligned");
+  DecodeArgs a = {};
+  a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.ck = (const bf16*)ck; a.cv = (const bf16*)cv;
+  a.cu_k = cu_k; a.cu_c = cu_c; a.order = order;
+  a.g_slc = (const bf16*)g_slc; a.g_swa = (const bf16*)g_swa; a.g_cmp = (const bf16*)g_cmp;
+  a.o = (bf16*)o; a.o_cmp = (bf16*)o_cmp; a.o_slc = (bf16*)o_slc; a.o_swa = (bf16*)o_swa; a.lse = lse; a.idx = idx;
+  a.nseq = nseq; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.n_sel = n_sel; a.window = window; a.cblock = block; a.cstride = stride;
+  a.sel_block = sel_block; a.total_k = total_k; a.total_c = total_c; a.max_Tc = max_Tc; a.scale = scale;
+  return launch_decode(a, (cudaStream_t)stream);
 }
 
 // ---- helpers ------------------------------------------------------------------------------------------

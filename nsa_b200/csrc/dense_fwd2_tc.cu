@@ -213,6 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);
       uint32_t ck0 = 0, cv0 = 0, ic = 0;
       uint32_t pph[2] = {0, 0};   // p_full phases consumed per group
+      uint32_t npi[2] = {0, 0};   // items with P.V tiles so far, per group (= o_free phases the group will have arrived on)
       bool ok = true;
       const uint64_t dq_desc0 = umma_smem_desc(q_s, 0, 1024), dq_desc1 = umma_smem_desc(q_s + TILE, 0, 1024);
       const uint64_t dk_base = umma_smem_desc(k_ring, 0, 1024);
@@ -239,8 +240,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const uint32_t c = cv0 + i;
                 vs = c % (uint32_t)VST;
                 ready = mbar_try(v_full0 + 8 * vs, (c / (uint32_t)VST) & 1);
-                // the previous item's epilogue must have read O before the first P.V of this item overwrites it
-                if (ready && !pv_any[g] && ic > 0) ready = mbar_try(o_free0 + 8 * g, (ic - 1) & 1);
+                // the epilogue of the group's previous item with P.V tiles must have read O before this item's first
+                // P.V overwrites it (items without P.V tiles neither touch O nor arrive on o_free)
+                if (ready && !pv_any[g] && npi[g] > 0) ready = mbar_try(o_free0 + 8 * g, (npi[g] - 1) & 1);
               }
               if (ready) {
                 if (i < sc.nAttn) {
@@ -255,6 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                           "r"(idesc_pv), "r"((uint32_t)((pv_any[g] || ks) ? 1 : 0))
                         : "memory");
                   umma_commit(pv_done0 + 8 * g);
+                  if (!pv_any[g]) ++npi[g];
                   pv_any[g] = true;
                   const uint32_t bit = 1u << (i & 7);
                   if (v_cnt & bit) {
@@ -312,9 +315,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         ck0 += nt;
         cv0 += sc.nAttn;
         if (nt == 0) umma_commit(q_free);
-        // every item consumes exactly one phase of each group's o_free: items without a P.V tile wait here
-        for (int g = 0; g < 2; ++g)
-          if (ok && !pv_any[g] && ic > 0) ok = mbar_wait_abortable(o_free0 + 8 * g, (ic - 1) & 1, 110, abort_flag);
       }
     }
   } else {
@@ -573,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int e = 0; e < 16; ++e) outv[e] = make_uint4(0u, 0u, 0u, 0u);
         }
         tc_fence_before();
-        mbar_arrive(o_free);
+        if (pv_local > 0) mbar_arrive(o_free);   // O has been read: the next item with P.V tiles may overwrite it
         if (live && ok) {
           uint4* dst = reinterpret_cast<uint4*>(a.o + orow * D);
 #pragma unroll

@@ -113,6 +113,33 @@ int kv_status(int* out);
 int launch_kv_bwd_tc(const KvArgs& a, cudaStream_t s);
 int kv_tc_status(int* out);
 
+// ---- batched decode (one new query token per sequence of a packed cache; decode.cu) ------------------------------
+struct DecodeArgs {
+  const bf16* q;        // [nseq,Hq,D]
+  const bf16* k;        // [total_k,Hkv,D]
+  const bf16* v;
+  const bf16* ck;       // [total_c,Hkv,D] compressed cache
+  const bf16* cv;
+  const int* cu_k;      // [nseq+1] device
+  const int* cu_c;      // [nseq+1] device
+  const int* order;     // [nseq] device: order in which the sequences are dealt to the CTAs (longest first), or null
+  const bf16* g_slc;    // [nseq,Hq] gates or null (= 1)
+  const bf16* g_swa;
+  const bf16* g_cmp;
+  bf16* o;              // [nseq,Hq,D] gated sum
+  bf16* o_cmp;          // branch outputs, each may be null
+  bf16* o_slc;
+  bf16* o_swa;
+  float* lse;           // [3,nseq,Hq] (compressed, selected, window) or null
+  int* idx;             // [nseq,Hkv,n_sel]
+  int nseq, Hq, Hkv, D, n_sel, window, cblock, cstride, sel_block;
+  long long total_k, total_c;
+  int max_Tc;
+  float scale;
+};
+int launch_decode(const DecodeArgs& a, cudaStream_t s);
+int decode_status(int* out);
+
 // ---- compression ------------------------------------------------------------------------------
 struct CompressArgs {
   const bf16* x;        // [tok,H,D]

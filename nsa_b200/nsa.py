@@ -151,6 +151,16 @@ class NSAAttention(nn.Module):
         bs = cu_seqlens_k.numel() - 1
         num_q_head, head_qk_dim = q.shape[1:]
         num_token, num_kv_head, head_v_dim = v.shape
+        if bs > 1 and (max_seqlen is None or bs * int(max_seqlen) != num_token):
+            # Sequences of different lengths (the reference's reshape at nsa/nsa.py:97 cannot take them): every sequence
+            # is one equal-length call on its slice of the packed tensors.  Costs one host read of cu_seqlens.
+            cu = [int(c) for c in cu_seqlens_k.tolist()]
+            if any(b - a != cu[1] - cu[0] for a, b in zip(cu[:-1], cu[1:])):
+                outs = []
+                for a, b in zip(cu[:-1], cu[1:]):
+                    one = torch.tensor([0, b - a], dtype=torch.int32, device=q.device)
+                    outs.append(self.forward(q[a:b], k[a:b], v[a:b], one, b - a, None, None, causal))
+                return torch.cat(outs, 0)
         scale = self.softmax_scale
         if scale is None or scale is True:
             # the reference's own callers pass `True` here positionally (tests/test_nsa_module.py:25), which its

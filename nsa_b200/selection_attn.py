@@ -6,14 +6,26 @@ import torch
 from . import _lib
 
 
+def _sequences(offsets, T):
+    """[(start, end)] of the packed sequences: one host read of cu_seqlens, or the whole tensor when there are none."""
+    if offsets is None:
+        return None
+    cu = [int(c) for c in (offsets.tolist() if torch.is_tensor(offsets) else offsets)]
+    if cu[0] != 0 or cu[-1] != T or any(b <= a for a, b in zip(cu[:-1], cu[1:])):
+        raise ValueError("cu_seqlens must start at 0, end at the token count %d and increase: %s" % (T, cu))
+    return list(zip(cu[:-1], cu[1:]))
+
+
 class ParallelNSAFunction(torch.autograd.Function):
     """Drop-in for ``ParallelNSAFunction`` (nsa/selection_attn.py:679-737):
-    apply(q, k, v, block_indices, block_counts, block_size, window_size, scale, offsets) -> (o_slc, o_swa)."""
+    apply(q, k, v, block_indices, block_counts, block_size, window_size, scale, offsets) -> (o_slc, o_swa).
+
+    With ``offsets`` (= cu_seqlens, batch size 1) the tokens are packed sequences of different lengths; block indices
+    and the causal / window masks are relative to each sequence's own start, as in the reference's varlen indexing
+    (nsa/selection_attn.py:419-425).  Each sequence is one launch chain on its slice of the packed tensors."""
 
     @staticmethod
     def forward(ctx, q, k, v, block_indices, block_counts, block_size, window_size, scale, offsets):
-        if offsets is not None:
-            raise NotImplementedError("variable-length sequences (cu_seqlens) are not supported by this operator yet")
         q = _lib.require(q, "q")
         k = _lib.require(k, "k")
         v = _lib.require(v, "v")
@@ -26,22 +38,29 @@ class ParallelNSAFunction(torch.autograd.Function):
         counts = None
         if torch.is_tensor(block_counts):
             counts = block_counts.to(torch.int32).contiguous()
+        seqs = _sequences(offsets, T)
+        if seqs is not None and B != 1:
+            raise ValueError("batch size must be 1 when cu_seqlens are provided")
         o_slc = torch.empty_like(q)
         lse_slc = torch.empty(B, T, Hq, dtype=torch.float32, device=q.device)
         o_swa = torch.empty_like(q) if window_size > 0 else None
         lse_swa = torch.empty_like(lse_slc) if window_size > 0 else None
-        _lib.check(_lib.lib().nsa_sel_swa_fwd(
-            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(idx), 1 if idx.dtype == torch.int64 else 0, _lib.ptr(counts),
-            _lib.ptr(o_slc), _lib.ptr(lse_slc), _lib.ptr(o_swa), _lib.ptr(lse_swa), None, None, None, None, None,
-            B, T, Hq, Hkv, D, S, block_size, window_size, float(scale), _lib.stream()), "nsa_sel_swa_fwd")
+        P, i64 = _lib.ptr, 1 if idx.dtype == torch.int64 else 0
+        for a, b in (seqs or [(0, T)]):
+            sl = slice(a, b)
+            _lib.check(_lib.lib().nsa_sel_swa_fwd(
+                P(q[:, sl]), P(k[:, sl]), P(v[:, sl]), P(idx[:, sl]), i64, P(counts[:, sl]) if counts is not None else None,
+                P(o_slc[:, sl]), P(lse_slc[:, sl]), P(o_swa[:, sl]) if o_swa is not None else None,
+                P(lse_swa[:, sl]) if lse_swa is not None else None, None, None, None, None, None,
+                B, b - a, Hq, Hkv, D, S, block_size, window_size, float(scale), _lib.stream()), "nsa_sel_swa_fwd")
         ctx.save_for_backward(q, k, v, o_slc, lse_slc, o_swa, lse_swa, idx, counts)
-        ctx.meta = (block_size, window_size, float(scale))
+        ctx.meta = (block_size, window_size, float(scale), seqs)
         return o_slc, o_swa
 
     @staticmethod
     def backward(ctx, do_slc, do_swa):
         q, k, v, o_slc, lse_slc, o_swa, lse_swa, idx, counts = ctx.saved_tensors
-        block_size, window_size, scale = ctx.meta
+        block_size, window_size, scale, seqs = ctx.meta
         B, T, Hq, D = q.shape
         Hkv, S = k.shape[2], idx.shape[-1]
         L = _lib.lib()
@@ -62,14 +81,18 @@ class ParallelNSAFunction(torch.autograd.Function):
         else:
             do_swa = None
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        ws_bytes = L.nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, S, block_size)
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-        _lib.check(L.nsa_sel_swa_bwd(
-            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(idx), 1 if idx.dtype == torch.int64 else 0, _lib.ptr(counts),
-            _lib.ptr(do_slc), _lib.ptr(lse_slc), _lib.ptr(delta_slc), None,
-            _lib.ptr(do_swa), _lib.ptr(lse_swa), _lib.ptr(delta_swa), None,
-            _lib.ptr(dq), 0, _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(ws), ws_bytes,
-            B, T, Hq, Hkv, D, S, block_size, window_size, scale, _lib.stream()), "nsa_sel_swa_bwd")
+        P, i64 = _lib.ptr, 1 if idx.dtype == torch.int64 else 0
+        opt = lambda t, sl: P(t[:, sl]) if t is not None else None
+        for a, b in (seqs or [(0, T)]):
+            sl = slice(a, b)
+            ws_bytes = L.nsa_sel_swa_bwd_workspace_bytes(B, b - a, Hkv, S, block_size)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+            _lib.check(L.nsa_sel_swa_bwd(
+                P(q[:, sl]), P(k[:, sl]), P(v[:, sl]), P(idx[:, sl]), i64, opt(counts, sl),
+                P(do_slc[:, sl]), P(lse_slc[:, sl]), P(delta_slc[:, sl]), None,
+                opt(do_swa, sl), opt(lse_swa, sl), opt(delta_swa, sl), None,
+                P(dq[:, sl]), 0, P(dk[:, sl]), P(dv[:, sl]), P(ws), ws_bytes,
+                B, b - a, Hq, Hkv, D, S, block_size, window_size, scale, _lib.stream()), "nsa_sel_swa_bwd")
         return dq, dk, dv, None, None, None, None, None, None
 
 

@@ -315,6 +315,15 @@ def nsa_decode_row(q_row, k, v, wk, bk, wv, bv, wg, bg, *, stride=16, block=32, 
         cv = compress_conv(v.unsqueeze(0), wv, bv, block, stride)[0]
     ck, cv = ck.float(), cv.float()
     Tc = ck.shape[0]
+    if Tc == 0:
+        # shorter than one compression block: no compressed key, nothing to select; only the window branch is left
+        k0 = max(0, t - window + 1)
+        ss = torch.einsum("hd,shd->hs", qf * scale, k[k0:].float().repeat_interleave(G, 1))
+        o_swa = torch.einsum("hs,shd->hd", torch.softmax(ss, -1), v[k0:].float().repeat_interleave(G, 1))
+        gate = qf @ wg.float().t() + bg.float()
+        o = o_swa * gate[:, 1:2]
+        idx = torch.zeros(Hkv, 0, dtype=torch.long)
+        return (o, idx, qf.new_zeros(Hkv, 0)) if return_scores else (o, idx)
     ckr, cvr = ck.repeat_interleave(G, 1), cv.repeat_interleave(G, 1)      # [Tc,Hq,D]
     raw = torch.einsum("hd,shd->hs", qf, ckr)
     vis = torch.arange(Tc) * stride + block <= t
@@ -329,7 +338,7 @@ def nsa_decode_row(q_row, k, v, wk, bk, wv, bv, wg, bg, *, stride=16, block=32, 
         lo = blk * ps - pp
         hi = min(lo + pk, Tc + pp)
         sc[:, blk] = psel[:, max(lo, 0):min(hi, Tc)].sum(-1) / (hi - lo)
-    idx = torch.argsort(-sc, dim=-1, stable=True)[:, :n_sel]              # [Hkv,n]
+    idx = torch.argsort(-sc, dim=-1, stable=True)[:, :min(n_sel, nb)]      # [Hkv,n] (fewer when fewer blocks exist)
     o_slc = qf.new_zeros(Hq, D)
     for h in range(Hkv):
         pos = (idx[h].unsqueeze(1) * sel_block + torch.arange(sel_block)).reshape(-1)

@@ -153,6 +153,67 @@ def test_selection_and_window_fwd_bwd(nsa, D, BS, S, Hq, Hkv, T, window):
     nsa._lib.device_status()
 
 
+def test_selection_varlen_cu_seqlens(nsa):
+    """parallel_nsa with cu_seqlens (packed sequences of different lengths, batch 1): block indices and masks are
+    relative to each sequence, as in the reference's varlen indexing (nsa/selection_attn.py:419-425).  Forward and
+    backward against the oracle evaluated sequence by sequence."""
+    gen = torch.Generator().manual_seed(99)
+    D, BS, S, Hq, Hkv, window = 128, 64, 4, 32, 2, 100
+    lens = [130, 384, 77]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    q, k, v = (_r(torch.randn(1, T, h, D, generator=gen)) for h in (Hq, Hkv, Hkv))
+    g_slc, g_swa = (_r(torch.rand(1, T, Hq, generator=gen)) for _ in range(2))
+    do = _r(torch.randn(1, T, Hq, D, generator=gen))
+    idx = torch.cat([_rand_indices(1, n, Hkv, S, BS, gen, poison=False) for n in lens], 1)
+    qd, kd, vd = (_dev(x).requires_grad_(True) for x in (q, k, v))
+    o = nsa.selection_attention(qd, kd, vd, _dev(g_slc), _dev(g_swa), idx.to(DEV), None, BS, window,
+                                cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV))
+    o.backward(_dev(do))
+    qo, ko, vo = (x.clone().requires_grad_(True) for x in (q, k, v))
+    refs = []
+    for a, b in zip(cu[:-1], cu[1:]):
+        r = O.parallel_nsa(qo[:, a:b], ko[:, a:b], vo[:, a:b], g_slc[:, a:b], g_swa[:, a:b], idx[:, a:b], None, BS, window)
+        (r * do[:, a:b]).sum().backward()
+        refs.append(r.detach())
+    _close("varlen o", o, torch.cat(refs, 1))
+    _close("varlen dq", qd.grad, qo.grad)
+    _close("varlen dk", kd.grad, ko.grad, scaled=True)
+    _close("varlen dv", vd.grad, vo.grad, scaled=True)
+    nsa._lib.device_status()
+
+
+def test_module_takes_sequences_of_different_lengths(nsa):
+    """NSAAttention.forward on packed sequences of unequal lengths equals the per-sequence calls (outputs and gradients)."""
+    gen = torch.Generator().manual_seed(98)
+    D, Hq, Hkv = 128, 16, 1
+    lens = [320, 512]
+    T = sum(lens)
+    q, k, v = (_dev(_r(torch.randn(T, h, D, generator=gen))) for h in (Hq, Hkv, Hkv))
+    do = _dev(_r(torch.randn(T, Hq, D, generator=gen)))
+    mod = nsa.NSAAttention(D, True, selected_block_count=3, sliding_window=64, device=DEV, dtype=torch.bfloat16)
+    cu = torch.tensor([0, lens[0], T], dtype=torch.int32, device=DEV)
+    qa, ka, va = (x.clone().requires_grad_(True) for x in (q, k, v))
+    out = mod(qa, ka, va, cu, max(lens))
+    out.backward(do)
+    wgrad = mod.gating.weight.grad.clone()
+    mod.zero_grad()
+    outs, grads = [], []
+    for a, b in ((0, lens[0]), (lens[0], T)):
+        qb, kb, vb = (x[a:b].clone().requires_grad_(True) for x in (q, k, v))
+        ob = mod(qb, kb, vb, torch.tensor([0, b - a], dtype=torch.int32, device=DEV), b - a)
+        ob.backward(do[a:b])
+        outs.append(ob.detach())
+        grads.append((qb.grad, kb.grad, vb.grad))
+    assert torch.equal(out.detach(), torch.cat(outs, 0))
+    for i, name in enumerate(("dq", "dk", "dv")):
+        assert torch.equal((qa.grad, ka.grad, va.grad)[i], torch.cat([g[i] for g in grads], 0)), name
+    _close("ragged d gating.weight", wgrad, mod.gating.weight.grad, atol=4e-2, scaled=True)
+    nsa._lib.device_status()
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,T,block,stride,causal", [(128, 32, 2, 520, 32, 16, True), (64, 16, 1, 333, 64, 16, True),
                                                             (128, 32, 2, 520, 32, 16, False),
                                                             (64, 16, 1, 333, 64, 16, False)])
@@ -401,9 +462,12 @@ def test_selection_full_size_properties(nsa):
 # ------------------------------------------------------------------------------------------------------
 # query shards (context parallelism): the kernels run on a slice of the queries against the whole K/V
 # ------------------------------------------------------------------------------------------------------
-def test_query_shards_match_unsharded_run(nsa):
+@pytest.mark.parametrize("prefix", [False, True])
+def test_query_shards_match_unsharded_run(nsa, prefix):
     """Emulates 2 ranks with the zig-zag layout on one GPU: four query chunks run one after the other through the
-    sharded entry points; outputs, selected indices and dQ must equal the unsharded run, dK/dV/dCK/dCV must sum to it."""
+    sharded entry points; outputs, selected indices and dQ must equal the unsharded run, dK/dV/dCK/dCV must sum to it.
+    With ``prefix`` a chunk is given only the keys up to its own last token (what the context-parallel wrapper
+    passes): nothing later can be attended, so the results are the same."""
     from nsa_b200.nsa import _NSACore
     gen = torch.Generator().manual_seed(77)
     B, T, Hq, Hkv, D, n_sel, window = 1, 1024, 32, 2, 128, 4, 128
@@ -416,11 +480,16 @@ def test_query_shards_match_unsharded_run(nsa):
 
     def run(q0, Tq):
         sl = slice(q0, q0 + Tq)
-        leaves = [t.clone().requires_grad_(True) for t in (q[:, sl].contiguous(), k, v, ck, cv, wg, bg)]
+        end = q0 + Tq if prefix else T
+        leaves = [t.clone().requires_grad_(True) for t in (q[:, sl].contiguous(), k[:, :end].contiguous(),
+                                                           v[:, :end].contiguous(), ck, cv, wg, bg)]
         cfg = (16, 32, True, D ** -0.5, 5, 4, 0, n_sel, 64, window, q0)
         o = _NSACore.apply(*leaves, cfg)
         o.backward(do[:, sl].contiguous())
-        return o.detach(), [t.grad for t in leaves]
+        grads = [t.grad for t in leaves]
+        for i in (1, 2):     # dk, dv of a key prefix: zero beyond it
+            grads[i] = torch.cat([grads[i], grads[i].new_zeros(B, T - end, Hkv, D)], 1)
+        return o.detach(), grads
 
     o_full, g_full = run(0, T)
     chunk = T // 4
@@ -474,7 +543,7 @@ def test_decode_rows_match_oracle(nsa):
     from nsa_b200.decode import compress_cache, nsa_decode
     gen = torch.Generator().manual_seed(404)
     Hq, Hkv, D, n_sel, window = 32, 2, 128, 3, 64
-    lens = [300, 1061, 2048, 517]
+    lens = [300, 1061, 2048, 517, 20, 40, 95]      # incl. shorter than one compression block and not multiples of 64
     cu = [0]
     for n in lens:
         cu.append(cu[-1] + n)
@@ -497,11 +566,43 @@ def test_decode_rows_match_oracle(nsa):
     wg, bg = mod.gating.weight.detach().float().cpu(), mod.gating.bias.detach().float().cpu()
     for i, L in enumerate(lens):
         ks, vs = k[cu[i]:cu[i + 1]], v[cu[i]:cu[i + 1]]
-        _close("ck of sequence %d" % i, ck[cu_c[i]:cu_c[i + 1]], O.compress_conv(ks.unsqueeze(0), wk, bk, 32, 16)[0])
+        if L >= 32:
+            _close("ck of sequence %d" % i, ck[cu_c[i]:cu_c[i + 1]], O.compress_conv(ks.unsqueeze(0), wk, bk, 32, 16)[0])
         # the row itself, evaluated by the oracle on the kernel's compressed cache (bf16) so that near-tie selections
         # do not confound the comparison; gates as the bf16 tensors the module produces
         ref, ref_idx, sc = O.nsa_decode_row(q[i], ks, vs, wk, bk, wv, bv, wg, bg, n_sel=n_sel, window=window,
                                             ck=ck[cu_c[i]:cu_c[i + 1]].cpu(), cv=cv[cu_c[i]:cu_c[i + 1]].cpu(),
                                             return_scores=True)
-        _close("decode row %d" % i, o[i], ref, atol=3e-2)
+        _close("decode row %d (L=%d)" % (i, L), o[i], ref, atol=3e-2)
+    nsa._lib.device_status()
+
+
+def test_decode_cache_extension(nsa):
+    """Appending tokens: the extended cache equals a cache compressed from scratch, and a decode step on it equals the
+    stateless step (only the compressed positions completed by the new tokens are computed)."""
+    from nsa_b200.decode import compress_cache, extend_compress_cache, nsa_decode
+    gen = torch.Generator().manual_seed(405)
+    Hq, Hkv, D = 32, 2, 128
+    old, grow = [300, 47, 31, 1024], [1, 17, 40, 0]
+    new = [a + b for a, b in zip(old, grow)]
+    cu_old, cu_new = [0], [0]
+    for a, b in zip(old, new):
+        cu_old.append(cu_old[-1] + a)
+        cu_new.append(cu_new[-1] + b)
+    k_new = _dev(_r(torch.randn(cu_new[-1], Hkv, D, generator=gen)))
+    v_new = _dev(_r(torch.randn(cu_new[-1], Hkv, D, generator=gen)))
+    take = torch.cat([torch.arange(cu_new[i], cu_new[i] + old[i]) for i in range(len(old))]).to(DEV)
+    k_old, v_old = k_new[take].contiguous(), v_new[take].contiguous()
+    mod = nsa.NSAAttention(D, True, selected_block_count=3, sliding_window=64, device=DEV, dtype=torch.bfloat16)
+    cache = compress_cache(mod, k_old, v_old, cu_old)
+    ext = extend_compress_cache(mod, cache, k_new, v_new, cu_new)
+    full = compress_cache(mod, k_new, v_new, cu_new)
+    assert ext.cu_c == full.cu_c
+    # (the appended positions come from the equal-length tcgen05 kernel, the from-scratch cache from the ragged one: the
+    # same contraction summed in a different order, so entries may differ by one bf16 rounding step)
+    _close("extended ck", ext.ck, full.ck, atol=1.6e-2, rtol=0)
+    _close("extended cv", ext.cv, full.cv, atol=1.6e-2, rtol=0)
+    q = _dev(_r(torch.randn(len(old), Hq, D, generator=gen)))
+    _close("decode on the extended cache", nsa_decode(mod, q, k_new, v_new, cu_new, cache=ext),
+           nsa_decode(mod, q, k_new, v_new, cu_new))
     nsa._lib.device_status()
