@@ -64,7 +64,7 @@ int nsa_device_status(void) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(1000 + (int)e, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
   int worst = 0, v = 0;
-  int (*fns[])(int*) = {sel_status, sel_block_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_tc_status, dense_dq_tc_status, gather_probe_status, dense_tc2_status, decode_status};
+  int (*fns[])(int*) = {sel_status, sel_block_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_dq_tc_status, gather_probe_status, dense_tc2_status, decode_status};
   for (auto f : fns) {
     v = 0;
     const int rc = f(&v);

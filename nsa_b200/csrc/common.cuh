@@ -217,6 +217,18 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test of a phase.  mbarrier.try_wait may suspend the thread for a system-dependent time when the phase is
+// not complete; a thread that polls SEVERAL barriers (the MMA issuer's event loop, a producer that serves two rings)
+// must not sleep on one of them while another is ready, so such loops use test_wait.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false (and records `code`) if the phase did not complete in ~2 s.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
   if (mbar_try(bar, parity)) return true;

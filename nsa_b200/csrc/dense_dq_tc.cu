@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           bool progressed = false;
           if (ns < sc.n) {
             const uint32_t cc = c0 + ns;
-            if (mbar_try(full0 + 8 * (cc & 1), (cc >> 1) & 1) && (cc == 0 || mbar_try(sdp_free, (cc - 1) & 1))) {
+            if (mbar_test(full0 + 8 * (cc & 1), (cc >> 1) & 1) && (cc == 0 || mbar_test(sdp_free, (cc - 1) & 1))) {
               tc_fence_after();
               issue_sdp(cc);
               if (ns == sc.n - 1) umma_commit(q_free);   // every S/dP of the item issued: Q and dO may be reloaded after them
@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           if (nd < ns) {
             const uint32_t cc = c0 + nd;
-            if (mbar_try(ds_full, cc & 1)) {
+            if (mbar_test(ds_full, cc & 1)) {
               tc_fence_after();
               const uint64_t dkm = (cc & 1) ? dkmn_desc1 : dkmn_desc0;
 #pragma unroll

@@ -42,6 +42,8 @@ struct Sched {
   int first, nA, nAttn, nB;
 };
 
+
+
 template <int MODE>
 __device__ __forceinline__ Sched make_sched(const DenseArgs& a, int t0) {
   Sched s;
@@ -64,6 +66,24 @@ __device__ __forceinline__ Sched make_sched(const DenseArgs& a, int t0) {
   return s;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// max over 128 values: four independent chains of three-input maxima (FMNMX runs at half rate; a single chain of 128
+// dependent two-input maxima cost ~600 cycles per tile)
+__device__ __forceinline__ float max128(const float (&s)[128]) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int e = 0; e < 128; e += 8) {
+    m0 = max3(m0, s[e], s[e + 1]);
+    m1 = max3(m1, s[e + 2], s[e + 3]);
+    m2 = max3(m2, s[e + 4], s[e + 5]);
+    m3 = max3(m3, s[e + 6], s[e + 7]);
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
 struct Fused {          // optional fused epilogues (null pointers switch them off)
   const bf16* gate_w;   // mode 1: [3, D] gate projection weight; rows: selected, window, compressed
   const bf16* gate_b;   // [3] or null
@@ -166,11 +186,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t vs = cv % (uint32_t)VST, vph = (cv / (uint32_t)VST) & 1;
         int act = 0;
         if (lane == 0) {
-          if (ik < nt && mbar_try(k_empty0 + 8 * ks, kph ^ 1)) {
+          if (ik < nt && mbar_test(k_empty0 + 8 * ks, kph ^ 1)) {
             mbar_expect_tx(k_full0 + 8 * ks, TILE);
             act |= 1;
           }
-          if (iv < sc.nAttn && mbar_try(v_empty0 + 8 * vs, vph ^ 1)) {
+          if (iv < sc.nAttn && mbar_test(v_empty0 + 8 * vs, vph ^ 1)) {
             mbar_expect_tx(v_full0 + 8 * vs, TILE);
             act |= 2;
           }
@@ -234,15 +254,15 @@ __global__ void __launch_bounds__(kThreads, 1)
             // (1) the group's P (or its "S has been read") of tile ip[g]
             if (ip[g] < is[g]) {
               const int i = ip[g];
-              bool ready = mbar_try(p_full0 + 8 * g, pph[g] & 1);
+              bool ready = mbar_test(p_full0 + 8 * g, pph[g] & 1);
               uint32_t vs = 0;
               if (ready && i < sc.nAttn) {
                 const uint32_t c = cv0 + i;
                 vs = c % (uint32_t)VST;
-                ready = mbar_try(v_full0 + 8 * vs, (c / (uint32_t)VST) & 1);
+                ready = mbar_test(v_full0 + 8 * vs, (c / (uint32_t)VST) & 1);
                 // the epilogue of the group's previous item with P.V tiles must have read O before this item's first
                 // P.V overwrites it (items without P.V tiles neither touch O nor arrive on o_free)
-                if (ready && !pv_any[g] && npi[g] > 0) ready = mbar_try(o_free0 + 8 * g, (npi[g] - 1) & 1);
+                if (ready && !pv_any[g] && npi[g] > 0) ready = mbar_test(o_free0 + 8 * g, (npi[g] - 1) & 1);
               }
               if (ready) {
                 if (i < sc.nAttn) {
@@ -276,7 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (is[g] < nt && ip[g] == is[g]) {
               const int i = is[g];
               const uint32_t c = ck0 + i, ks_ = c % (uint32_t)KST;
-              if (mbar_try(k_full0 + 8 * ks_, (c / (uint32_t)KST) & 1)) {
+              if (mbar_test(k_full0 + 8 * ks_, (c / (uint32_t)KST) & 1)) {
                 tc_fence_after();
                 const uint64_t dk = umma_desc_advance(dk_base, ks_ * TILE);
                 const uint64_t dq = g ? dq_desc1 : dq_desc0;
@@ -395,34 +415,36 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int c = 0; c < 8; ++c) tmem_ld16(s_col + c * 16, *reinterpret_cast<float(*)[16]>(&s[c * 16]));
         tmem_ld_wait();
 
-        if (do_sel && !passB) {
-          // statistics of the raw-score soft-max; only the last tile can hold columns past Lk
+        const bool attn_tile = i < sc.nAttn;
+        if (!attn_tile) {
+          // nothing is written back for this tile: the scores are in registers, so S of the group's next tile may be
+          // issued now and runs under the arithmetic below
+          tc_fence_before();
+          mbar_arrive(p_full);
+        }
+        if (do_sel) {
+          // columns past Lk exist only in the last tile; rows past Tq contribute nothing to the scores
           const int nval = min(128, a.Lk - j0);
-          float mx = -INFINITY;
-          if (nval >= 128) {
-#pragma unroll
-            for (int e = 0; e < 128; ++e) mx = fmaxf(mx, s[e]);
-          } else {
+          if (nval < 128) {
 #pragma unroll
             for (int e = 0; e < 128; ++e)
-              if (e < nval) mx = fmaxf(mx, s[e]);
+              if (e >= nval) s[e] = -INFINITY;
           }
-          const float mnew = fmaxf(m2, mx);
+        }
+        if (do_sel && !passB) {
+          // statistics of the raw-score soft-max over all compressed keys
+          const float mnew = fmaxf(m2, max128(s));
           if (mnew > -INFINITY) {
             const float nm = -mnew * kLog2e;
-            float rs0 = 0.f, rs1 = 0.f;
-            if (nval >= 128) {
+            float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
-              for (int e = 0; e < 128; e += 2) {
-                rs0 += ex2(fmaf(s[e], kLog2e, nm));
-                rs1 += ex2(fmaf(s[e + 1], kLog2e, nm));
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 128; ++e)
-                if (e < nval) rs0 += ex2(fmaf(s[e], kLog2e, nm));
+            for (int e = 0; e < 128; e += 4) {
+              rs0 += ex2(fmaf(s[e], kLog2e, nm));
+              rs1 += ex2(fmaf(s[e + 1], kLog2e, nm));
+              rs2 += ex2(fmaf(s[e + 2], kLog2e, nm));
+              rs3 += ex2(fmaf(s[e + 3], kLog2e, nm));
             }
-            l2 = l2 * ex2((m2 - mnew) * kLog2e) + (rs0 + rs1);
+            l2 = l2 * ex2((m2 - mnew) * kLog2e) + ((rs0 + rs1) + (rs2 + rs3));
             m2 = mnew;
           }
         }
@@ -431,20 +453,17 @@ __global__ void __launch_bounds__(kThreads, 1)
           // first column of block k+1), then sum the 16 heads of the token with a halving butterfly: after four
           // exchange steps every lane of the 16 holds two of the 32 sums.  Done per half of 64 columns.
           const float nm = -sel_m * kLog2e;
+          const float inv_b = live ? sel_inv : 0.f;
           float* pt = gpool + tl * pool_floats;
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             const int jh = j0 + hh * 64;
-            const int nval = live ? min(64, a.Lk - jh) : 0;
             float v[32];   // v[k] = columns 4k..4k+3, v[16+k] = column 4k
 #pragma unroll
             for (int k = 0; k < 16; ++k) {
               float pe[4];
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const int e = 4 * k + u;
-                pe[u] = (e < nval) ? ex2(fmaf(s[hh * 64 + e], kLog2e, nm)) * sel_inv : 0.f;
-              }
+              for (int u = 0; u < 4; ++u) pe[u] = ex2(fmaf(s[hh * 64 + 4 * k + u], kLog2e, nm)) * inv_b;   // masked columns: 0
               v[k] = (pe[0] + pe[1]) + (pe[2] + pe[3]);
               v[16 + k] = pe[0];
             }
@@ -487,7 +506,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
-        if (i < sc.nAttn) {
+        if (attn_tile) {
           // ---- attention soft-max of this tile: valid columns form one interval [lo, hi) ----------------------
           int lo = 0, hi = 128;
           if (MODE == 0) {
@@ -498,17 +517,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           if (!live) hi = 0;
           const bool full = (lo <= 0) && (hi >= 128);
-          float mx = -INFINITY;
-          if (full) {
+          if (!full) {
 #pragma unroll
-            for (int e = 0; e < 128; ++e) mx = fmaxf(mx, s[e]);
-          } else {
-#pragma unroll
-            for (int e = 0; e < 128; ++e) {
+            for (int e = 0; e < 128; ++e)
               if (e < lo || e >= hi) s[e] = -INFINITY;
-              mx = fmaxf(mx, s[e]);
-            }
           }
+          float mx = max128(s);
           mx *= sl2;   // sl2 > 0: the maximum of the scaled scores
           // Lazy rescale: the reference maximum follows the true maximum only when that has grown by more than 2^8
           // (log2 domain), so exponentials stay below 256 and the TMEM round trip that rescales O is rare.
@@ -531,26 +545,33 @@ __global__ void __launch_bounds__(kThreads, 1)
               tmem_st16(o_col + c * 16, o);
             }
           }
-          float rs0 = 0.f, rs1 = 0.f;
+          float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {   // 32 keys -> 16 packed columns per store
             float pk[16];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
+            for (int e = 0; e < 16; e += 2) {
               const float p0 = ex2(fmaf(s[c * 32 + 2 * e], sl2, -muse)), p1 = ex2(fmaf(s[c * 32 + 2 * e + 1], sl2, -muse));
-              rs0 += p0;
-              rs1 += p1;
+              const float p2 = ex2(fmaf(s[c * 32 + 2 * e + 2], sl2, -muse)), p3 = ex2(fmaf(s[c * 32 + 2 * e + 3], sl2, -muse));
+              rs0 += p0; rs1 += p1; rs2 += p2; rs3 += p3;
               pk[e] = __uint_as_float(pack_bf16(p0, p1));
+              pk[e + 1] = __uint_as_float(pack_bf16(p2, p3));
             }
             tmem_st16(s_col + c * 16, pk);
           }
+          rs0 = (rs0 + rs1) + (rs2 + rs3);
+          rs1 = 0.f;
           l_run = l_run * alpha + (rs0 + rs1);
           tmem_st_wait();
           ++npv;
           ++pv_local;
         }
-        tc_fence_before();
-        mbar_arrive(p_full);   // P is in place (or, for a statistics-only tile, S has been read)
+        if (attn_tile) {
+          tc_fence_before();
+          mbar_arrive(p_full);   // P is in place
+        }
+        if (gthread == 0) {
+        }
       }
       // ---- epilogue of the item ----------------------------------------------------------------------
       {
@@ -624,30 +645,28 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             __syncwarp();
             int* out = a.sel_idx + (((long long)b * a.Tq + tt) * HG + hg) * a.n_sel;
+            // Pooled scores are >= 0, so their bit patterns order like the values: one integer warp reduction finds the
+            // maximum, a second the lowest block index that holds it (ties go to the lower index).
             for (int r = 0; r < a.n_sel; ++r) {
-              float bv = -2.f;
+              unsigned bv = 0u;
               int bi = 0x7fffffff;
+              bool any = false;
               for (int blk = lane; blk < a.n_pool; blk += 32) {
                 const float v = pt[blk];
-                if (v > bv) {
-                  bv = v;
-                  bi = blk;
+                if (v >= 0.f) {
+                  const unsigned u = __float_as_uint(v);
+                  if (!any || u > bv) {
+                    bv = u;
+                    bi = blk;
+                  }
+                  any = true;
                 }
               }
-#pragma unroll
-              for (int off = 16; off > 0; off >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-                if (ov > bv || (ov == bv && oi < bi)) {
-                  bv = ov;
-                  bi = oi;
-                }
-              }
-              const bool found = bv > -1.5f;
-              if (lane == 0) {
-                out[r] = found ? bi : -1;
-                if (found) pt[bi] = -2.f;
-              }
+              const unsigned key = any ? bv + 1u : 0u;                         // 0 = this lane has no candidate left
+              const unsigned best = __reduce_max_sync(0xffffffffu, key);
+              const int win = __reduce_min_sync(0xffffffffu, (key == best && any) ? bi : 0x7fffffff);
+              if (lane == 0) out[r] = best ? win : -1;
+              if (best && (win & 31) == lane) pt[win] = -2.f;                  // the owner lane retires the block
               __syncwarp();
             }
           }
@@ -698,6 +717,15 @@ int launch(const DenseArgs& a, const Fused& fu, cudaStream_t s) {
 
 }  // namespace
 
+// True when the tcgen05 forward covers this configuration (otherwise the caller uses launch_dense_fwd).
+bool dense_fwd_tc_supported(const DenseArgs& a, int head_dim) {
+  if (head_dim != 128) return false;
+  if (a.mode == 1 && a.n_sel > 0) {
+    if (a.pool_k != 5 || a.pool_s != 4 || a.pool_p != 0) return false;
+    if (a.n_pool > kMaxPool) return false;
+  }
+  return true;
+}
 int launch_dense_fwd2_tc(const DenseArgs& a, cudaStream_t s) {
   Fused fu = {};
   fu.gate_w = a.gate_w;

@@ -78,9 +78,7 @@ int launch_dense_dq(const DenseArgs& a, int D, cudaStream_t s);
 int dense_status(int* out);
 // tcgen05 forward for head_dim 128 (and, for selection, the 5/4/0 pooling of the default block sizes)
 bool dense_fwd_tc_supported(const DenseArgs& a, int head_dim);
-int launch_dense_fwd_tc(const DenseArgs& a, cudaStream_t s);
-int dense_tc_status(int* out);
-// two query tiles per CTA, P kept in tensor memory (dense_fwd2_tc.cu); same support matrix as dense_fwd_tc_supported
+// two query tiles per CTA, P kept in tensor memory (dense_fwd2_tc.cu)
 int launch_dense_fwd2_tc(const DenseArgs& a, cudaStream_t s);
 int dense_tc2_status(int* out);
 int launch_dense_dq_tc(const DenseArgs& a, cudaStream_t s);

@@ -245,14 +245,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint64_t t_idle = 0;
       while (ok && nd < nb) {
         bool progressed = false;
-        if (ns < nb && ns < nd + 2 && mbar_try(full0 + 8 * (ns % kStages), (ns / kStages) & 1) &&
-            (ns < 2 || mbar_try(sdp_free + 8 * (ns & 1), ((ns >> 1) - 1) & 1))) {
+        if (ns < nb && ns < nd + 2 && mbar_test(full0 + 8 * (ns % kStages), (ns / kStages) & 1) &&
+            (ns < 2 || mbar_test(sdp_free + 8 * (ns & 1), ((ns >> 1) - 1) & 1))) {
           tc_fence_after();
           issue_sdp(ns);
           ++ns;
           progressed = true;
         }
-        if (nd < ns && mbar_try(pds_full + 8 * (nd & 1), (nd >> 1) & 1)) {
+        if (nd < ns && mbar_test(pds_full + 8 * (nd & 1), (nd >> 1) & 1)) {
           tc_fence_after();
           issue_dkv(nd);
           ++nd;
