@@ -154,6 +154,25 @@ int nsa_sel_swa_bwd_sharded(const void* q, const void* k, const void* v, const v
                             size_t ws_bytes, int B, int T, int Hq, int Hkv, int D, int S, int BS, int window,
                             float scale, int Tq, int q0, void* stream);
 
+/* The two backward entry points above with the row pre-pass folded in (what nsa_rowdot / nsa_rowdot3 compute): instead of
+ * taking delta, they take the branch outputs saved by the forward and the ONE upstream gradient `dout` of the gated sum
+ * o = g_slc*o_slc + g_swa*o_swa + g_cmp*o_cmp (nsa/nsa.py:133), and they WRITE, per branch x, delta_x = g_x * rowsum(o_x *
+ * dout) (fp32 [B,Tq,Hq], also used internally) and dgate_x = rowsum(o_x * dout) (bf16 [B,Tq,Hq], the gate gradient; NULL to
+ * skip).  With head_dim 128 the sums are formed inside the tcgen05 dQ kernels while the dO tile is resident (the window
+ * kernel serves the selected branch too and runs before it), so o_x and dout are not read by a separate pass; other
+ * configurations run the pre-pass kernel first.  Replaces, in addition, parallel_nsa_bwd_kernel_preprocess
+ * (nsa/selection_attn.py:520-530), _attn_bwd_preprocess (nsa/triton_attention.py:184-199) and the gate-product gradients
+ * of nsa/nsa.py:133.  Tq = T, q0 = 0 for an unsharded call. */
+int nsa_sel_swa_bwd_fused(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                          const void* o_slc, const void* o_swa, const void* dout, const float* lse_slc, float* delta_slc,
+                          const void* gate_slc, void* dgate_slc, const float* lse_swa, float* delta_swa, const void* gate_swa,
+                          void* dgate_swa, void* dq, int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B,
+                          int T, int Hq, int Hkv, int D, int S, int BS, int window, float scale, int Tq, int q0, void* stream);
+int nsa_cmp_attn_bwd_fused(const void* q, const void* ck, const void* cv, const void* o_cmp, const float* lse, const void* dout,
+                           float* delta, const void* gate, void* dgate, void* dq, int accumulate_dq, void* dck, void* dcv,
+                           void* ws, size_t ws_bytes, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride,
+                           int causal, float scale, int Tq, int q0, void* stream);
+
 /* ---- decode ---------------------------------------------------------------------------------------------
  * No entry point of the reference does this (its module assumes len(q) == len(k), nsa/nsa.py:97); it is the
  * module's forward (nsa/nsa.py:94-135) for ONE new query token per sequence, at position L-1 of a packed, ragged

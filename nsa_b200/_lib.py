@@ -38,6 +38,8 @@ SIGNATURES = {
     "nsa_sel_swa_fwd_sharded": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P]),
     "nsa_sel_swa_bwd_sharded": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I,
                                     F, I, I, P]),
+    "nsa_sel_swa_bwd_fused": (I, [P, P, P, P, I, P] + [P] * 11 + [P, I, P, P, P, Z, I, I, I, I, I, I, I, I, F, I, I, P]),
+    "nsa_cmp_attn_bwd_fused": (I, [P] * 10 + [I, P, P, P, Z, I, I, I, I, I, I, I, I, I, F, I, I, P]),
     "nsa_gather_probe": (I, [P, P, P, I, I, I, I, I, I, I, I, P]),
     "nsa_decode_fwd": (I, [P] * 17 + [I, L, L, I, I, I, I, I, I, I, I, I, F, P]),
     "nsa_rowdot": (I, [P, P, P, P, P, L, I, P]),

@@ -220,10 +220,15 @@ size_t nsa_cmp_attn_bwd_workspace_bytes(int B, int T, int Tc, int Hk, int D) {
   return (size_t)2 * nseg * B * Tc * Hk * D * sizeof(float);
 }
 
+struct PreCmp {   // row pre-pass folded into the compressed branch's dQ kernel
+  const void* o_cmp;
+  void* dg_cmp;
+};
+
 static int cmp_attn_bwd_impl(const void* q, const void* ck, const void* cv, const float* lse, const void* dout,
                      const float* delta, const void* gate, void* dq, int accumulate_dq, void* dck, void* dcv, void* ws,
                      size_t ws_bytes, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
-                     float scale, int Tq, int q0, void* stream) {
+                     float scale, int Tq, int q0, void* stream, const PreCmp* pre = nullptr) {
   const bool sharded = (Tq != T) || (q0 != 0);
   if (Tq <= 0 || q0 < 0 || q0 + Tq > T) return fail(-12, "%s: query shard [%d, %d) is outside the sequence of %d tokens", "nsa_cmp_attn_bwd", q0, q0 + Tq, T);
   (void)sharded;
@@ -231,8 +236,22 @@ static int cmp_attn_bwd_impl(const void* q, const void* ck, const void* cv, cons
   int rc = check_attn_shape("nsa_cmp_attn_bwd", B, T, Hq, Hk, D);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
+  bool fold = false;
+  if (pre) {
+    if (!pre->o_cmp) return fail(-1, "nsa_cmp_attn_bwd_fused: o_cmp is null");
+    fold = dq && D == 128;
+    if (!fold) {   // no tcgen05 dQ kernel to carry the pre-pass: run it on its own
+      rc = launch_rowdot((const bf16*)pre->o_cmp, (const bf16*)dout, (const bf16*)gate, const_cast<float*>(delta),
+                         (bf16*)pre->dg_cmp, (long long)B * Tq * Hq, D, s);
+      if (rc) return rc;
+    }
+  }
   if (dq) {
     DenseArgs a = {};
+    if (fold) {
+      a.pre_o[0] = (const bf16*)pre->o_cmp; a.pre_gate[0] = (const bf16*)gate; a.pre_delta[0] = const_cast<float*>(delta);
+      a.pre_dgate[0] = (bf16*)pre->dg_cmp;
+    }
     a.mode = 1; a.q = (const bf16*)q; a.k = (const bf16*)ck; a.v = (const bf16*)cv; a.lse = const_cast<float*>(lse);
     a.dout = (const bf16*)dout; a.delta = delta; a.gate = (const bf16*)gate; a.dq = (bf16*)dq;
     a.accumulate = accumulate_dq; a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.cblock = block;
@@ -312,16 +331,7 @@ static int sel_swa_fwd_impl(const void* q, const void* k, const void* v, const v
     a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.o = (bf16*)o_swa; a.lse = lse_swa;
     a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
     if (!dense_fwd_tc_supported(a, D) && sharded) return fail(-11, "query shards need head_dim 128");
-    if (dense_fwd_tc_supported(a, D)) {
-      if (o) {   // the gated sum of the branches is written by the window kernel's epilogue
-        a.comb_o = (bf16*)o; a.comb_slc = (const bf16*)o_slc; a.comb_cmp = (const bf16*)o_cmp;
-        a.comb_g[0] = (const bf16*)g_slc; a.comb_g[1] = (const bf16*)g_swa; a.comb_g[2] = (const bf16*)g_cmp;
-        o = nullptr;
-      }
-      rc = launch_dense_fwd2_tc(a, s);
-    } else {
-      rc = launch_dense_fwd(a, D, s);
-    }
+    rc = dense_fwd_tc_supported(a, D) ? launch_dense_fwd2_tc(a, s) : launch_dense_fwd(a, D, s);
     if (rc) return rc;
   }
   if (o) {
@@ -346,6 +356,14 @@ int nsa_sel_swa_fwd_sharded(const void* q, const void* k, const void* v, const v
   return sel_swa_fwd_impl(q, k, v, idx, idx64, counts, o_slc, lse_slc, o_swa, lse_swa, g_slc, g_swa, o_cmp, g_cmp, o, B, T, Hq, Hkv, D, S, BS, window, scale, Tq, q0, stream);
 }
 
+int nsa_cmp_attn_bwd_fused(const void* q, const void* ck, const void* cv, const void* o_cmp, const float* lse, const void* dout,
+                           float* delta, const void* gate, void* dgate, void* dq, int accumulate_dq, void* dck, void* dcv,
+                           void* ws, size_t ws_bytes, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride,
+                           int causal, float scale, int Tq, int q0, void* stream) {
+  const PreCmp pre = {o_cmp, dgate};
+  return cmp_attn_bwd_impl(q, ck, cv, lse, dout, delta, gate, dq, accumulate_dq, dck, dcv, ws, ws_bytes, B, T, Tc, Hq, Hk, D, block, stride, causal, scale, Tq, q0, stream, &pre);
+}
+
 size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS) {
   if (BS <= 0) return 0;
   const size_t NB = (size_t)(T + BS - 1) / BS;
@@ -353,11 +371,17 @@ size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS) {
   return align_up(bh * NB * NB * 4, 256) + align_up(bh * (NB + 1) * 4, 256) + align_up(bh * (size_t)T * S * 4, 256);
 }
 
+struct PreSel {   // row pre-pass of the selected and window branches folded into the window's dQ kernel
+  const void *o_slc, *o_swa;
+  void *dg_slc, *dg_swa;
+};
+
 static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
                     const void* dout_slc, const float* lse_slc, const float* delta_slc, const void* gate_slc,
                     const void* dout_swa, const float* lse_swa, const float* delta_swa, const void* gate_swa, void* dq,
                     int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
-                    int D, int S, int BS, int window, float scale, int Tq, int q0, void* stream) {
+                    int D, int S, int BS, int window, float scale, int Tq, int q0, void* stream,
+                    const PreSel* pre = nullptr) {
   const bool sharded = (Tq != T) || (q0 != 0);
   if (Tq <= 0 || q0 < 0 || q0 + Tq > T) return fail(-12, "%s: query shard [%d, %d) is outside the sequence of %d tokens", "nsa_sel_swa_bwd", q0, q0 + Tq, T);
   (void)sharded;
@@ -371,8 +395,46 @@ static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const v
   if (has_slc && (!idx || !lse_slc || !delta_slc)) return fail(-1, "nsa_sel_swa_bwd: selected branch inputs missing");
   if (has_swa && (!lse_swa || !delta_swa)) return fail(-1, "nsa_sel_swa_bwd: window branch inputs missing");
   cudaStream_t s = (cudaStream_t)stream;
+  const long long rows = (long long)B * Tq * Hq;
+  bool fold = false;
+  if (pre) {
+    if ((has_slc && !pre->o_slc) || (has_swa && !pre->o_swa)) return fail(-1, "nsa_sel_swa_bwd_fused: a branch output is null");
+    if (has_slc && has_swa && dout_slc != dout_swa)
+      return fail(-15, "nsa_sel_swa_bwd_fused: both branches must share one upstream gradient (the module's dO)");
+    // the window's tcgen05 dQ kernel carries the pre-pass of both branches and therefore runs first
+    fold = dq && has_swa && D == 128;
+    if (!fold) {
+      const bf16* o3[3] = {has_slc ? (const bf16*)pre->o_slc : nullptr, has_swa ? (const bf16*)pre->o_swa : nullptr, nullptr};
+      const bf16* g3[3] = {(const bf16*)gate_slc, (const bf16*)gate_swa, nullptr};
+      float* d3[3] = {const_cast<float*>(delta_slc), const_cast<float*>(delta_swa), nullptr};
+      bf16* dg3[3] = {(bf16*)pre->dg_slc, (bf16*)pre->dg_swa, nullptr};
+      rc = launch_rowdot3(o3, (const bf16*)(has_slc ? dout_slc : dout_swa), g3, d3, dg3, rows, D, s);
+      if (rc) return rc;
+    }
+  }
   if (dq) {
     int acc = accumulate_dq;
+    auto run_swa = [&]() -> int {
+      DenseArgs a = {};
+      a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.lse = const_cast<float*>(lse_swa);
+      a.dout = (const bf16*)dout_swa; a.delta = delta_swa; a.gate = (const bf16*)gate_swa; a.dq = (bf16*)dq;
+      a.accumulate = acc; a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
+      if (fold) {
+        a.pre_o[0] = (const bf16*)pre->o_swa; a.pre_gate[0] = (const bf16*)gate_swa;
+        a.pre_delta[0] = const_cast<float*>(delta_swa); a.pre_dgate[0] = (bf16*)pre->dg_swa;
+        if (has_slc) {
+          a.pre_o[1] = (const bf16*)pre->o_slc; a.pre_gate[1] = (const bf16*)gate_slc;
+          a.pre_delta[1] = const_cast<float*>(delta_slc); a.pre_dgate[1] = (bf16*)pre->dg_slc;
+        }
+      }
+      if (D != 128 && sharded) return fail(-11, "query shards need head_dim 128");
+      return (D == 128) ? launch_dense_dq_tc(a, s) : launch_dense_dq(a, D, s);
+    };
+    if (fold) {
+      rc = run_swa();
+      if (rc) return rc;
+      acc = 1;
+    }
     if (has_slc) {
       SelArgs a = {};
       a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64; a.counts = counts;
@@ -383,13 +445,8 @@ static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const v
       if (rc) return rc;
       acc = 1;
     }
-    if (has_swa) {
-      DenseArgs a = {};
-      a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.lse = const_cast<float*>(lse_swa);
-      a.dout = (const bf16*)dout_swa; a.delta = delta_swa; a.gate = (const bf16*)gate_swa; a.dq = (bf16*)dq;
-      a.accumulate = acc; a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.window = window; a.scale = scale;
-      if (D != 128 && sharded) return fail(-11, "query shards need head_dim 128");
-      rc = (D == 128) ? launch_dense_dq_tc(a, s) : launch_dense_dq(a, D, s);
+    if (has_swa && !fold) {
+      rc = run_swa();
       if (rc) return rc;
     }
   }
@@ -453,6 +510,17 @@ int nsa_gather_probe(const void* k, const void* v, const void* idx, int idx64, i
   a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64;
   a.B = B; a.T = T; a.Tq = T; a.q0 = 0; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS;
   return launch_gather_probe(a, D, (cudaStream_t)stream);
+}
+
+int nsa_sel_swa_bwd_fused(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                          const void* o_slc, const void* o_swa, const void* dout, const float* lse_slc, float* delta_slc,
+                          const void* gate_slc, void* dgate_slc, const float* lse_swa, float* delta_swa, const void* gate_swa,
+                          void* dgate_swa, void* dq, int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B,
+                          int T, int Hq, int Hkv, int D, int S, int BS, int window, float scale, int Tq, int q0, void* stream) {
+  if (!dout || !delta_slc) return fail(-1, "nsa_sel_swa_bwd_fused: null pointer");
+  if (window > 0 && !delta_swa) return fail(-1, "nsa_sel_swa_bwd_fused: delta_swa is null");
+  const PreSel pre = {o_slc, o_swa, dgate_slc, dgate_swa};
+  return sel_swa_bwd_impl(q, k, v, idx, idx64, counts, dout, lse_slc, delta_slc, gate_slc, window > 0 ? dout : nullptr, lse_swa, delta_swa, gate_swa, dq, accumulate_dq, dk, dv, ws, ws_bytes, B, T, Hq, Hkv, D, S, BS, window, scale, Tq, q0, stream, &pre);
 }
 
 // ---- decode ---------------------------------------------------------------------------------------------

@@ -26,7 +26,7 @@ constexpr uint32_t TILE = 2 * PANEL;          // 32 KB
 constexpr uint32_t STAGE = 2 * TILE;          // K + V
 constexpr int kStages = 2;
 constexpr uint32_t kTmemCols = 512;           // S 0..127, dP 128..255, dQ 256..383
-constexpr uint32_t kSmem = 2 * TILE + kStages * STAGE + TILE + 256 + 1024;
+constexpr uint32_t kSmem = 2 * TILE + kStages * STAGE + TILE + 256 + 1024 + 1024;   // + [2][128] floats of the row pre-pass
 
 struct Sched {
   int first, n;
@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                  sdp_free = misc + 56, ds_full = misc + 64, ds_free = misc + 72, dq_full = misc + 80, dq_free = misc + 88,
                  tmem_slot = misc + 96;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + (misc - sbase) + 104);
+  float* xpre = reinterpret_cast<float*>(sgen + (misc - sbase) + 256);   // [2 branches][128 rows] exchange of the row pre-pass
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
@@ -244,8 +245,59 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (MODE == 1 && a.causal) nvis = (t < a.cblock) ? 0 : min(a.Lk, (t - a.cblock) / a.cstride + 1);
       const long long qrow = ((long long)b * a.Tq + (live ? tloc : 0)) * a.Hq + hg * 16 + head;
       const float lse2 = a.lse[qrow] * kLog2e;
-      const float del = a.delta[qrow];
       const float gv = a.gate ? __bfloat162float(a.gate[qrow]) : 1.f;
+      float del;
+      if (a.pre_o[0]) {
+        // Row pre-pass folded in (parallel_nsa_bwd_kernel_preprocess, nsa/selection_attn.py:520-530; _attn_bwd_preprocess,
+        // nsa/triton_attention.py:184-199; the gate gradients of nsa/nsa.py:133): rowsum(o_x * dO) over this thread's 64
+        // channels, the two halves of a row meet in shared memory, the first half finishes and publishes the row's delta.
+        float part[2] = {0.f, 0.f};
+        const uint4* pd = reinterpret_cast<const uint4*>(a.dout + qrow * D + half * 64);
+        uint4 dv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dv[e] = pd[e];
+#pragma unroll
+        for (int br = 0; br < 2; ++br) {
+          if (!a.pre_o[br]) continue;
+          const uint4* po = reinterpret_cast<const uint4*>(a.pre_o[br] + qrow * D + half * 64);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const uint4 ov = po[e];
+            const __nv_bfloat162* ho2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+            const __nv_bfloat162* hd2 = reinterpret_cast<const __nv_bfloat162*>(&dv[e]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float2 x = __bfloat1622float2(ho2[u]), y = __bfloat1622float2(hd2[u]);
+              part[br] = fmaf(x.x, y.x, fmaf(x.y, y.y, part[br]));
+            }
+          }
+        }
+        if (half == 1) {
+          xpre[row] = part[0];
+          xpre[128 + row] = part[1];
+        }
+        named_bar_sync(1, kSoft);
+        if (half == 0) {
+          float own = 0.f;
+#pragma unroll
+          for (int br = 0; br < 2; ++br) {
+            if (!a.pre_o[br]) continue;
+            const float tot = part[br] + xpre[br * 128 + row];
+            const float gb = a.pre_gate[br] ? __bfloat162float(a.pre_gate[br][qrow]) : 1.f;
+            if (live) {
+              a.pre_delta[br][qrow] = gb * tot;
+              if (a.pre_dgate[br]) a.pre_dgate[br][qrow] = __float2bfloat16(tot);
+            }
+            if (br == 0) own = gb * tot;
+          }
+          xpre[row] = own;
+          del = own;
+        }
+        named_bar_sync(1, kSoft);
+        if (half == 1) del = xpre[row];
+      } else {
+        del = a.delta[qrow];
+      }
       const bool dead = !live || !(lse2 > -INFINITY);
       // the row's previous dq (accumulate mode) is fetched now, so its latency hides behind the tile loop instead of
       // stalling the epilogue (measured: ~1000 of ~5000 cycles per tile)

@@ -1,8 +1,8 @@
 // Dense query-major attention FORWARD on tcgen05, two query tiles per CTA (head_dim 128): sliding-window attention
 // (mode 0) and compressed attention with the fused block selection (mode 1).  Semantics and result layouts of
 // nsa/selection_attn.py:484-516 (window), nsa/triton_attention.py:87-181,465-475 (compressed attention, scores, top-n,
-// with the scoring of nsa/torch_attention.py:121-125) and, as optional fused epilogues, the gate projection
-// nn.Linear(head_dim, 3) of nsa/nsa.py:117 and the gated three-branch sum of nsa/nsa.py:133.
+// with the scoring of nsa/torch_attention.py:121-125) and, optionally, the gate projection nn.Linear(head_dim, 3) of
+// nsa/nsa.py:117 computed from the resident query tiles.
 //
 // A persistent CTA owns 16 consecutive tokens x the 16 heads of a GQA group = two [128 x 128] Q tiles that share one
 // stream of [128 keys x 128] K and V tiles (K and V in separate mbarrier rings, so a K slot is recycled as soon as
@@ -84,14 +84,10 @@ __device__ __forceinline__ float max128(const float (&s)[128]) {
   }
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
-struct Fused {          // optional fused epilogues (null pointers switch them off)
+struct Fused {          // optional gate projection (null pointers switch it off)
   const bf16* gate_w;   // mode 1: [3, D] gate projection weight; rows: selected, window, compressed
   const bf16* gate_b;   // [3] or null
   bf16* g_out[3];       // [B*Tq*Hq] each
-  bf16* comb_o;         // mode 0: o = g0*o_slc + g1*o_swa + g2*o_cmp
-  const bf16* comb_slc;
-  const bf16* comb_cmp;
-  const bf16* comb_g[3];
 };
 
 template <int MODE>
@@ -600,32 +596,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int e = 0; e < 16; ++e) dst[e] = outv[e];
           a.lse[orow] = l_run > 0.f ? (m_run + log2f(l_run)) * kLn2 : -INFINITY;
-          if (MODE == 0 && fu.comb_o) {
-            // gated three-branch sum: o = g_slc*o_slc + g_swa*o_swa + g_cmp*o_cmp, with o_swa taken as stored (bf16)
-            const float g0 = fu.comb_g[0] ? __bfloat162float(fu.comb_g[0][orow]) : 1.f;
-            const float g1 = fu.comb_g[1] ? __bfloat162float(fu.comb_g[1][orow]) : 1.f;
-            const float g2 = fu.comb_g[2] ? __bfloat162float(fu.comb_g[2][orow]) : 1.f;
-            const uint4* ps = fu.comb_slc ? reinterpret_cast<const uint4*>(fu.comb_slc + orow * D) : nullptr;
-            const uint4* pc = fu.comb_cmp ? reinterpret_cast<const uint4*>(fu.comb_cmp + orow * D) : nullptr;
-            uint4* po = reinterpret_cast<uint4*>(fu.comb_o + orow * D);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              uint4 xs = make_uint4(0u, 0u, 0u, 0u), xc = make_uint4(0u, 0u, 0u, 0u);
-              if (ps) xs = ps[e];
-              if (pc) xc = pc[e];
-              const __nv_bfloat162* hs = reinterpret_cast<const __nv_bfloat162*>(&xs);
-              const __nv_bfloat162* hc = reinterpret_cast<const __nv_bfloat162*>(&xc);
-              const __nv_bfloat162* hw = reinterpret_cast<const __nv_bfloat162*>(&outv[e]);
-              uint4 res;
-              __nv_bfloat162* hr = reinterpret_cast<__nv_bfloat162*>(&res);
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const float2 fs = __bfloat1622float2(hs[u]), fc = __bfloat1622float2(hc[u]), fw = __bfloat1622float2(hw[u]);
-                hr[u] = __floats2bfloat162_rn(g0 * fs.x + g1 * fw.x + g2 * fc.x, g0 * fs.y + g1 * fw.y + g2 * fc.y);
-              }
-              po[e] = res;
-            }
-          }
         }
       }
       if (do_sel) {
@@ -730,13 +700,7 @@ int launch_dense_fwd2_tc(const DenseArgs& a, cudaStream_t s) {
   Fused fu = {};
   fu.gate_w = a.gate_w;
   fu.gate_b = a.gate_b;
-  for (int i = 0; i < 3; ++i) {
-    fu.g_out[i] = a.g_out[i];
-    fu.comb_g[i] = a.comb_g[i];
-  }
-  fu.comb_o = a.comb_o;
-  fu.comb_slc = a.comb_slc;
-  fu.comb_cmp = a.comb_cmp;
+  for (int i = 0; i < 3; ++i) fu.g_out[i] = a.g_out[i];
   return a.mode == 0 ? launch<0>(a, fu, s) : launch<1>(a, fu, s);
 }
 int dense_tc2_status(int* out) {

@@ -64,14 +64,17 @@ struct DenseArgs {
   int* sel_idx;        // [B,T,Hq/16,n_sel] int32
   float* sel_scores;   // optional [B,Hq/16,T,n_pool] fp32 dump of the pooled scores, or null
   int Tq, q0;          // query shard: q-indexed tensors hold Tq rows per batch, row i is sequence position q0+i
-  // optional fused epilogues of the two-tile tcgen05 forward (null = off)
+  // optional, two-tile tcgen05 forward: the module's gate projection computed from the resident query tiles (null = off)
   const bf16* gate_w;  // mode 1: [3,D] gate projection weight (rows: selected, window, compressed); writes g_out
   const bf16* gate_b;  // [3] or null
   bf16* g_out[3];      // [B,Tq,Hq] each
-  bf16* comb_o;        // mode 0: comb_o = comb_g[0]*comb_slc + comb_g[1]*o + comb_g[2]*comb_cmp (null tensor: term dropped)
-  const bf16* comb_slc;
-  const bf16* comb_cmp;
-  const bf16* comb_g[3];
+  // optional, dQ kernels (tcgen05): the row pre-pass of the backward folded in.  With pre_o[0] set the kernel computes
+  // rowsum(o * dO) itself for its own branch ([0]) and, if given, a second branch ([1]) whose dQ kernel runs later:
+  // pre_delta[x] = gate_x * rowsum (fp32, also what this kernel uses as delta), pre_dgate[x] = rowsum (bf16, gate gradient)
+  const bf16* pre_o[2];
+  const bf16* pre_gate[2];
+  float* pre_delta[2];
+  bf16* pre_dgate[2];
 };
 int launch_dense_fwd(const DenseArgs& a, int D, cudaStream_t s);
 int launch_dense_dq(const DenseArgs& a, int D, cudaStream_t s);

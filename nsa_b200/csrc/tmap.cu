@@ -24,6 +24,14 @@ static void resolve() {
 static int encode(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
                   const cuuint32_t* box) {
   std::call_once(g_once, resolve);
+  // cuTensorMapEncodeTiled is a driver-API call and needs a context current on the calling thread.  PyTorch runs
+  // backward passes on worker threads that may not have touched the runtime yet when this is the first thing an entry
+  // point does, so the primary context of the thread's current device is bound here (a no-op afterwards).
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   if (!g_encode) {
     set_error("cuTensorMapEncodeTiled is not available from this driver");
     return -20;

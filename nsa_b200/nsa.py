@@ -17,8 +17,11 @@ class _NSACore(torch.autograd.Function):
     def forward(ctx, q, k, v, ck, cv, w_gate, b_gate, cfg):
         """q: [B,Tq,Hq,D] = the queries at sequence positions q0 .. q0+Tq-1; k, v: [B,T,Hkv,D] and ck, cv:
         [B,Tc,Hkv,D] cover the whole sequence; w_gate [3,D], b_gate [3]: the gate projection (rows: selected,
-        window, compressed; nsa/nsa.py:59,117).  cfg[-1] = q0 (0 and Tq == T for an unsharded call)."""
-        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window, q0) = cfg
+        window, compressed; nsa/nsa.py:59,117).  cfg[10] = q0 (0 and Tq == T for an unsharded call); an optional
+        cfg[11] = True folds the gate projection and the backward's row pre-pass into the attention kernels (fewer
+        launches; slower than the streaming kernels at large shapes, see NSAAttention.fuse_row_passes)."""
+        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window, q0) = cfg[:11]
+        fused = len(cfg) > 11 and bool(cfg[11])
         q, k, v, ck, cv = (_lib.require(t, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (ck, "ck"), (cv, "cv")))
         w_gate = _lib.require(w_gate, "gating.weight")
         b_gate = _lib.require(b_gate, "gating.bias") if b_gate is not None else None
@@ -35,11 +38,18 @@ class _NSACore(torch.autograd.Function):
         lse_cmp, lse_slc = (torch.empty(B, Tq, Hq, dtype=torch.float32, device=dev) for _ in range(2))
         lse_swa = torch.empty_like(lse_slc) if window > 0 else None
         idx = torch.empty(B, Tq, Hkv, n_sel, dtype=torch.int32, device=dev)
-        # compressed attention + block selection; the gate projection rides on the resident query tiles
-        _lib.check(L.nsa_cmp_attn_fwd_gated(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, P(w_gate), P(b_gate),
-                                            P(g_slc), P(g_swa), P(g_cmp), B, T, Tc, Hq, Hkv, D, block, stride,
-                                            1 if causal else 0, scale, n_sel, pool_k, pool_s, pool_p, Tq, q0, S()),
-                   "nsa_cmp_attn_fwd_gated")
+        if fused:
+            # compressed attention + block selection; the gate projection rides on the resident query tiles
+            _lib.check(L.nsa_cmp_attn_fwd_gated(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, P(w_gate),
+                                                P(b_gate), P(g_slc), P(g_swa), P(g_cmp), B, T, Tc, Hq, Hkv, D, block, stride,
+                                                1 if causal else 0, scale, n_sel, pool_k, pool_s, pool_p, Tq, q0, S()),
+                       "nsa_cmp_attn_fwd_gated")
+        else:
+            _lib.check(L.nsa_gate_fwd(P(q), P(w_gate), P(b_gate), P(g_slc), P(g_swa), P(g_cmp), B * Tq * Hq, D, S()),
+                       "nsa_gate_fwd")
+            _lib.check(L.nsa_cmp_attn_fwd_sharded(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, B, T, Tc, Hq, Hkv,
+                                                  D, block, stride, 1 if causal else 0, scale, n_sel, pool_k, pool_s,
+                                                  pool_p, Tq, q0, S()), "nsa_cmp_attn_fwd")
         _lib.check(L.nsa_sel_swa_fwd_sharded(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(lse_slc), P(o_swa),
                                              P(lse_swa), P(g_slc), P(g_swa), P(o_cmp), P(g_cmp), P(o), B, T, Hq, Hkv, D,
                                              n_sel, sel_block, window, scale, Tq, q0, S()), "nsa_sel_swa_fwd")
@@ -53,7 +63,8 @@ class _NSACore(torch.autograd.Function):
     def backward(ctx, do):
         (q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx,
          w_gate) = ctx.saved_tensors
-        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window, q0) = ctx.cfg
+        (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window, q0) = ctx.cfg[:11]
+        fused = len(ctx.cfg) > 11 and bool(ctx.cfg[11])
         do = _lib.require(do, "do")
         B, Tq, Hq, D = q.shape
         T, Hkv, Tc = k.shape[1], k.shape[2], ck.shape[1]
@@ -61,27 +72,41 @@ class _NSACore(torch.autograd.Function):
         dev = q.device
         rows = B * Tq * Hq
 
-        # one pass over dO: delta = g * rowsum(o * dO) and the gate gradients rowsum(o * dO) of all three branches
         delta_slc, delta_cmp = (torch.empty(B, Tq, Hq, dtype=torch.float32, device=dev) for _ in range(2))
         delta_swa = torch.empty_like(delta_slc) if window > 0 else None
         dg_slc, dg_swa, dg_cmp = (torch.empty_like(g_slc) for _ in range(3))
         if window <= 0:
             dg_swa.zero_()
-        _lib.check(L.nsa_rowdot3(P(o_slc), P(o_swa), P(o_cmp), P(do), P(g_slc), P(g_swa), P(g_cmp), P(delta_slc),
-                                 P(delta_swa), P(delta_cmp), P(dg_slc), P(dg_swa), P(dg_cmp), rows, D, S()), "nsa_rowdot3")
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dck, dcv = torch.empty_like(ck), torch.empty_like(cv)
         ws_bytes = L.nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, n_sel, sel_block)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        _lib.check(L.nsa_sel_swa_bwd_sharded(P(q), P(k), P(v), P(idx), 0, None, P(do), P(lse_slc), P(delta_slc), P(g_slc),
-                                             P(do) if window > 0 else None, P(lse_swa), P(delta_swa), P(g_swa), P(dq), 0,
-                                             P(dk), P(dv), P(ws), ws_bytes, B, T, Hq, Hkv, D, n_sel, sel_block, window,
-                                             scale, Tq, q0, S()), "nsa_sel_swa_bwd")
-        dck, dcv = torch.empty_like(ck), torch.empty_like(cv)
-        ws_bytes = L.nsa_cmp_attn_bwd_workspace_bytes(B, T, Tc, Hkv, D)
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        _lib.check(L.nsa_cmp_attn_bwd_sharded(P(q), P(ck), P(cv), P(lse_cmp), P(do), P(delta_cmp), P(g_cmp), P(dq), 1,
-                                              P(dck), P(dcv), P(ws), ws_bytes, B, T, Tc, Hq, Hkv, D, block, stride,
-                                              1 if causal else 0, scale, Tq, q0, S()), "nsa_cmp_attn_bwd")
+        ws2_bytes = L.nsa_cmp_attn_bwd_workspace_bytes(B, T, Tc, Hkv, D)
+        ws2 = torch.empty(ws2_bytes, dtype=torch.uint8, device=dev)
+        if fused:
+            # delta = g * rowsum(o * dO) and the gate gradients rowsum(o * dO) are formed inside the dQ kernels while the
+            # dO tile is resident (no separate pass over o_slc, o_swa, o_cmp and dO)
+            _lib.check(L.nsa_sel_swa_bwd_fused(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(o_swa), P(do), P(lse_slc),
+                                               P(delta_slc), P(g_slc), P(dg_slc), P(lse_swa), P(delta_swa), P(g_swa),
+                                               P(dg_swa) if window > 0 else None, P(dq), 0, P(dk), P(dv), P(ws), ws_bytes,
+                                               B, T, Hq, Hkv, D, n_sel, sel_block, window, scale, Tq, q0, S()),
+                       "nsa_sel_swa_bwd_fused")
+            _lib.check(L.nsa_cmp_attn_bwd_fused(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(do), P(delta_cmp), P(g_cmp),
+                                                P(dg_cmp), P(dq), 1, P(dck), P(dcv), P(ws2), ws2_bytes, B, T, Tc, Hq, Hkv, D,
+                                                block, stride, 1 if causal else 0, scale, Tq, q0, S()),
+                       "nsa_cmp_attn_bwd_fused")
+        else:
+            # one streaming pass over dO: delta = g * rowsum(o * dO) and the gate gradients of all three branches
+            _lib.check(L.nsa_rowdot3(P(o_slc), P(o_swa), P(o_cmp), P(do), P(g_slc), P(g_swa), P(g_cmp), P(delta_slc),
+                                     P(delta_swa), P(delta_cmp), P(dg_slc), P(dg_swa), P(dg_cmp), rows, D, S()),
+                       "nsa_rowdot3")
+            _lib.check(L.nsa_sel_swa_bwd_sharded(P(q), P(k), P(v), P(idx), 0, None, P(do), P(lse_slc), P(delta_slc),
+                                                 P(g_slc), P(do) if window > 0 else None, P(lse_swa), P(delta_swa), P(g_swa),
+                                                 P(dq), 0, P(dk), P(dv), P(ws), ws_bytes, B, T, Hq, Hkv, D, n_sel, sel_block,
+                                                 window, scale, Tq, q0, S()), "nsa_sel_swa_bwd")
+            _lib.check(L.nsa_cmp_attn_bwd_sharded(P(q), P(ck), P(cv), P(lse_cmp), P(do), P(delta_cmp), P(g_cmp), P(dq), 1,
+                                                  P(dck), P(dcv), P(ws2), ws2_bytes, B, T, Tc, Hq, Hkv, D, block, stride,
+                                                  1 if causal else 0, scale, Tq, q0, S()), "nsa_cmp_attn_bwd")
         # gate projection backward: dq += dg . W in place (dq is complete here), dW and db by fixed-order reduction
         dw = torch.empty_like(w_gate)
         db = torch.empty(3, dtype=w_gate.dtype, device=dev) if ctx.has_bias else None
@@ -134,6 +159,11 @@ class NSAAttention(nn.Module):
         self.pool_padding = compression_block // compression_stride - 2
         self.pool_stride = selection_block // compression_stride
         self.gating = nn.Linear(head_dim, 3, device=device, dtype=dtype)
+        # Not a constructor argument (the signature stays the reference's).  True folds the gate projection into the
+        # compressed-attention kernel and the backward's row pre-pass into the dQ kernels: three launches fewer per step,
+        # which pays for small, launch-bound shapes; at the benchmark's shape the separate streaming kernels are faster
+        # (they read rows fully coalesced; a thread-per-row epilogue does not), so the default is False.
+        self.fuse_row_passes = False
 
     def forward(
         self,
@@ -174,7 +204,7 @@ class NSAAttention(nn.Module):
         v4 = v.reshape(bs, -1, num_kv_head, head_v_dim)
         cfg = (self.compression_stride, self.compression_block, bool(causal), float(scale), self.pool_kernel_size,
                self.pool_stride, self.pool_padding, self.selected_block_count, self.selection_block_size,
-               self.sliding_window, 0)
+               self.sliding_window, 0, self.fuse_row_passes)
         # the gate projection (nn.Linear(head_dim, 3), no activation) runs inside the fused node
         o = _NSACore.apply(q4, k4, v4, ck, cv, self.gating.weight, self.gating.bias, cfg)
         return o.reshape(-1, *o.shape[-2:])

@@ -311,13 +311,17 @@ def _module_and_oracle(nsa, B, T, Hq, Hkv, D, n_sel, window, seed, causal=True):
     return mod, q, k, v, gen
 
 
-@pytest.mark.parametrize("D,Hq,Hkv,T,n_sel,window,causal", [(128, 32, 2, 1024, 4, 128, True), (64, 16, 1, 640, 3, 64, True),
-                                                            (128, 32, 2, 1024, 4, 128, False)])
-def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window, causal):
+@pytest.mark.parametrize("D,Hq,Hkv,T,n_sel,window,causal,fused", [(128, 32, 2, 1024, 4, 128, True, False),
+                                                                  (64, 16, 1, 640, 3, 64, True, False),
+                                                                  (128, 32, 2, 1024, 4, 128, False, False),
+                                                                  (128, 32, 2, 1024, 4, 128, True, True),
+                                                                  (64, 16, 1, 640, 3, 64, True, True)])
+def test_module_forward_backward(nsa, D, Hq, Hkv, T, n_sel, window, causal, fused):
     """``causal`` is the module's constructor flag (default False in the reference, nsa/nsa.py:18): it only changes
     the mask of the compressed branch; selected and sliding-window attention are causal either way."""
     B = 2
     mod, q, k, v, gen = _module_and_oracle(nsa, B, T, Hq, Hkv, D, n_sel, window, seed=31 + D, causal=causal)
+    mod.fuse_row_passes = fused      # the fused entry points (nsa_cmp_attn_fwd_gated, nsa_*_bwd_fused) or the streaming kernels
     cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
     qd, kd, vd = (_dev(x.reshape(B * T, *x.shape[2:])).requires_grad_(True) for x in (q, k, v))
     out = mod(qd, kd, vd, cu, T)
