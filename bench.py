@@ -774,9 +774,11 @@ def run_decode(args):
 
 
 def run_profile_case():
-    """B=1 slice of the workload (q, dO 134 MB each: larger than L2, well under 1 GB on the device)."""
+    """Small case for ncu: the B=1 slice of the workload (q, dO 134 MB each: larger than L2, well under 1 GB on the
+    device), every kernel family of the step launched twice, then two batched decode steps over 16 cached sequences."""
     import torch
     import nsa_b200
+    from nsa_b200.decode import compress_cache, nsa_decode
     c = CFG
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
@@ -788,7 +790,21 @@ def run_profile_case():
         for p in mod.parameters():
             p.copy_(torch.randn(p.shape, generator=gen) * 0.02)
         kern, keys = per_kernel_breakdown(torch, nsa_b200, mod, q, k, v, do, reps=1)
-    print(json.dumps({"profile_case": "B=1 T=8192 Hq=64 Hkv=4 D=128", "kernels_ms": kern, "selected_keys": keys}))
+        lens = decode_lengths()[:16]
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        g2 = torch.Generator(device=dev).manual_seed(4)
+        qd = torch.randn(len(lens), Hq, D, generator=g2, device=dev, dtype=torch.bfloat16)
+        kd = torch.randn(cu[-1], Hkv, D, generator=g2, device=dev, dtype=torch.bfloat16)
+        vd = torch.randn(cu[-1], Hkv, D, generator=g2, device=dev, dtype=torch.bfloat16)
+        cache = compress_cache(mod, kd, vd, cu)
+        for _ in range(2):
+            nsa_decode(mod, qd, kd, vd, cu, cache=cache)
+        torch.cuda.synchronize()
+    nsa_b200._lib.device_status()
+    print(json.dumps({"profile_case": "B=1 T=8192 Hq=64 Hkv=4 D=128; decode: 16 sequences, %d cached tokens" % cu[-1],
+                      "kernels_ms": kern, "selected_keys": keys}))
 
 
 def main():

@@ -180,16 +180,21 @@ int nsa_cmp_attn_bwd_fused(const void* q, const void* ck, const void* cv, const 
  * q, o [nseq,Hq,D]; k, v [total_k,Hkv,D]; ck, cv [total_c,Hkv,D] = the compressed cache (nsa_compress_fwd with the
  * Conv1d length rule Tc = (L-block)/stride + 1); cu_k, cu_c: DEVICE int32 [nseq+1] cumulative lengths of k/v and of
  * ck/cv; order: DEVICE int32 [nseq] = the order in which sequences are dealt to the CTAs (pass them longest first for
- * an even load) or NULL; gates [nseq,Hq] (NULL = 1).  Optional outputs (NULL to skip): the branch outputs o_cmp, o_slc,
+ * an even load) or NULL.  Gates: either gate_w [3,D] (+ gate_b [3] or NULL), the module's nn.Linear(head_dim, 3) whose rows
+ * are selected, window, compressed (nsa/nsa.py:59,117) -- the gates are then computed from q inside the call -- or, with
+ * gate_w NULL, precomputed g_slc, g_swa, g_cmp [nseq,Hq] (NULL = 1).  Optional outputs (NULL to skip): the branch outputs o_cmp, o_slc,
  * o_swa [nseq,Hq,D] and lse fp32 [3,nseq,Hq] (compressed, selected, window); idx int32 [nseq,Hkv,n_sel] receives the
  * selected blocks.  max_Tc = the largest per-sequence compressed length (host-known; at most 2048, i.e. caches up to
- * 32 K tokens).  Needs head_dim 128, 16 query heads per KV head, 64-key blocks, stride 16 / block 32.  No host
- * synchronisation, no internal streams: everything is enqueued on `stream`. */
+ * 32 K tokens).  ws: nsa_decode_workspace_bytes(nseq, Hkv) bytes of scratch (the per-warp partial results that a second,
+ * small kernel merges in a fixed order).  Needs head_dim 128, 16 query heads per KV head, 64-key blocks, stride 16 /
+ * block 32.  Two launches, no host synchronisation, no internal streams: everything is enqueued on `stream`. */
 int nsa_decode_fwd(const void* q, const void* k, const void* v, const void* ck, const void* cv, const int32_t* cu_k,
-                   const int32_t* cu_c, const int32_t* order, const void* g_slc, const void* g_swa, const void* g_cmp, void* o,
-                   void* o_cmp, void* o_slc, void* o_swa, float* lse, int32_t* idx, int nseq, long long total_k,
-                   long long total_c, int max_Tc, int Hq, int Hkv, int D, int block, int stride, int sel_block, int n_sel,
-                   int window, float scale, void* stream);
+                   const int32_t* cu_c, const int32_t* order, const void* gate_w, const void* gate_b, const void* g_slc,
+                   const void* g_swa, const void* g_cmp, void* o, void* o_cmp, void* o_slc, void* o_swa, float* lse,
+                   int32_t* idx, void* ws, size_t ws_bytes, int nseq,
+                   long long total_k, long long total_c, int max_Tc, int Hq, int Hkv, int D, int block, int stride,
+                   int sel_block, int n_sel, int window, float scale, void* stream);
+size_t nsa_decode_workspace_bytes(int nseq, int Hkv);
 
 /* ---- helpers --------------------------------------------------------------------------------------
  * delta[r] = (gate ? gate[r] : 1) * sum_d o[r,d]*dout[r,d] (fp32, NULL to skip) and

@@ -41,7 +41,8 @@ SIGNATURES = {
     "nsa_sel_swa_bwd_fused": (I, [P, P, P, P, I, P] + [P] * 11 + [P, I, P, P, P, Z, I, I, I, I, I, I, I, I, F, I, I, P]),
     "nsa_cmp_attn_bwd_fused": (I, [P] * 10 + [I, P, P, P, Z, I, I, I, I, I, I, I, I, I, F, I, I, P]),
     "nsa_gather_probe": (I, [P, P, P, I, I, I, I, I, I, I, I, P]),
-    "nsa_decode_fwd": (I, [P] * 17 + [I, L, L, I, I, I, I, I, I, I, I, I, F, P]),
+    "nsa_decode_fwd": (I, [P] * 20 + [Z, I, L, L, I, I, I, I, I, I, I, I, I, F, P]),
+    "nsa_decode_workspace_bytes": (Z, [I, I]),
     "nsa_rowdot": (I, [P, P, P, P, P, L, I, P]),
     "nsa_combine": (I, [P, P, P, P, P, P, P, L, I, P]),
     "nsa_gate_fwd": (I, [P, P, P, P, P, P, L, I, P]),

@@ -525,24 +525,28 @@ int nsa_sel_swa_bwd_fused(const void* q, const void* k, const void* v, const voi
 
 // ---- decode ---------------------------------------------------------------------------------------------
 int nsa_decode_fwd(const void* q, const void* k, const void* v, const void* ck, const void* cv, const int32_t* cu_k,
-                   const int32_t* cu_c, const int32_t* order, const void* g_slc, const void* g_swa, const void* g_cmp, void* o,
-                   void* o_cmp, void* o_slc, void* o_swa, float* lse, int32_t* idx, int nseq, long long total_k,
-                   long long total_c, int max_Tc, int Hq, int Hkv, int D, int block, int stride, int sel_block, int n_sel,
-                   int window, float scale, void* stream) {
-  if (!q || !k || !v || !ck || !cv || !cu_k || !cu_c || !o || !idx) return fail(-1, "nsa_decode_fwd: null pointer");
+                   const int32_t* cu_c, const int32_t* order, const void* gate_w, const void* gate_b, const void* g_slc,
+                   const void* g_swa, const void* g_cmp, void* o, void* o_cmp, void* o_slc, void* o_swa, float* lse,
+                   int32_t* idx, void* ws, size_t ws_bytes, int nseq,
+                   long long total_k, long long total_c, int max_Tc, int Hq, int Hkv, int D, int block, int stride,
+                   int sel_block, int n_sel, int window, float scale, void* stream) {
+  if (!q || !k || !v || !ck || !cv || !cu_k || !cu_c || !o || !idx || !ws) return fail(-1, "nsa_decode_fwd: null pointer");
   if (nseq <= 0) return 0;
   if (total_k <= 0 || total_c <= 0 || Hq <= 0 || Hkv <= 0) return fail(-1, "nsa_decode_fwd: empty shape");
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(ck) || !aligned16(cv) || !aligned16(o))
     return fail(-5, "nsa_decode_fwd: pointers must be 16-byte aligned");
   DecodeArgs a = {};
   a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.ck = (const bf16*)ck; a.cv = (const bf16*)cv;
-  a.cu_k = cu_k; a.cu_c = cu_c; a.order = order;
+  a.cu_k = cu_k; a.cu_c = cu_c; a.order = order; a.gate_w = (const bf16*)gate_w; a.gate_b = (const bf16*)gate_b;
   a.g_slc = (const bf16*)g_slc; a.g_swa = (const bf16*)g_swa; a.g_cmp = (const bf16*)g_cmp;
   a.o = (bf16*)o; a.o_cmp = (bf16*)o_cmp; a.o_slc = (bf16*)o_slc; a.o_swa = (bf16*)o_swa; a.lse = lse; a.idx = idx;
   a.nseq = nseq; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.n_sel = n_sel; a.window = window; a.cblock = block; a.cstride = stride;
   a.sel_block = sel_block; a.total_k = total_k; a.total_c = total_c; a.max_Tc = max_Tc; a.scale = scale;
+  a.part = (float*)ws; a.part_bytes = ws_bytes;
   return launch_decode(a, (cudaStream_t)stream);
 }
+
+size_t nsa_decode_workspace_bytes(int nseq, int Hkv) { return decode_workspace_bytes(nseq, Hkv); }
 
 // ---- helpers ------------------------------------------------------------------------------------------
 int nsa_rowdot(const void* o, const void* dout, const void* gate, float* delta, void* dgate, long long rows, int D,

@@ -124,7 +124,9 @@ struct DecodeArgs {
   const int* cu_k;      // [nseq+1] device
   const int* cu_c;      // [nseq+1] device
   const int* order;     // [nseq] device: order in which the sequences are dealt to the CTAs (longest first), or null
-  const bf16* g_slc;    // [nseq,Hq] gates or null (= 1)
+  const bf16* gate_w;   // [3,D] gate projection (rows: selected, window, compressed): gates computed from q; or null
+  const bf16* gate_b;   // [3] or null
+  const bf16* g_slc;    // [nseq,Hq] precomputed gates (used when gate_w is null), or null (= 1)
   const bf16* g_swa;
   const bf16* g_cmp;
   bf16* o;              // [nseq,Hq,D] gated sum
@@ -137,7 +139,10 @@ struct DecodeArgs {
   long long total_k, total_c;
   int max_Tc;
   float scale;
+  float* part;          // workspace of decode_workspace_bytes(): per (item, branch, consumer warp) partial results
+  size_t part_bytes;
 };
+size_t decode_workspace_bytes(int nseq, int Hkv);
 int launch_decode(const DecodeArgs& a, cudaStream_t s);
 int decode_status(int* out);
 

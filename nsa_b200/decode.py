@@ -27,6 +27,13 @@ class CompressedCache:
         self.order_dev = torch.tensor(sorted(range(n), key=lambda i: -lens[i]), dtype=torch.int32, device=dev)
         self.max_tc = max([self.cu_c[i + 1] - self.cu_c[i] for i in range(n)] + [0])
 
+    def workspace(self, nbytes):
+        """Scratch of the decode kernels (per-warp partial results), kept with the cache so a step allocates nothing."""
+        ws = getattr(self, "_ws", None)
+        if ws is None or ws.numel() < nbytes:
+            ws = self._ws = torch.empty(nbytes, dtype=torch.uint8, device=self.ck.device)
+        return ws
+
     def __iter__(self):   # (ck, cv, cu, cu_c), the tuple earlier callers unpack
         return iter((self.ck, self.cv, self.cu, self.cu_c))
 
@@ -116,8 +123,8 @@ def nsa_decode(module, q, k, v, cu_seqlens_k, cache=None, return_parts=False):
     scale = module.softmax_scale
     if scale is None or scale is True:
         scale = 1.0 if scale is True else D ** -0.5
-    gates = module.gating(q)
-    g_slc, g_swa, g_cmp = (g.contiguous() for g in gates.unbind(-1))
+    w_gate = _lib.require(module.gating.weight.detach(), "gating.weight")
+    b_gate = _lib.require(module.gating.bias.detach(), "gating.bias") if module.gating.bias is not None else None
     o = torch.empty_like(q)
     n_sel = module.selected_block_count
     idx = torch.empty(nseq, Hkv, n_sel, dtype=torch.int32, device=q.device)
@@ -125,11 +132,13 @@ def nsa_decode(module, q, k, v, cu_seqlens_k, cache=None, return_parts=False):
     if return_parts:
         o_cmp, o_slc, o_swa = (torch.empty_like(q) for _ in range(3))
         lse = torch.empty(3, nseq, Hq, dtype=torch.float32, device=q.device)
-    P = _lib.ptr
-    _lib.check(_lib.lib().nsa_decode_fwd(P(q), P(k), P(v), P(cache.ck), P(cache.cv), P(cache.cu_dev), P(cache.cu_c_dev),
-                                         P(cache.order_dev), P(g_slc), P(g_swa), P(g_cmp), P(o), P(o_cmp), P(o_slc),
-                                         P(o_swa), P(lse), P(idx), nseq, k.shape[0], cache.ck.shape[0], cache.max_tc, Hq,
-                                         Hkv, D, module.compression_block, module.compression_stride,
+    P, L = _lib.ptr, _lib.lib()
+    ws_bytes = L.nsa_decode_workspace_bytes(nseq, Hkv)
+    ws = cache.workspace(ws_bytes)
+    _lib.check(L.nsa_decode_fwd(P(q), P(k), P(v), P(cache.ck), P(cache.cv), P(cache.cu_dev), P(cache.cu_c_dev),
+                                         P(cache.order_dev), P(w_gate), P(b_gate), None, None, None, P(o), P(o_cmp), P(o_slc),
+                                         P(o_swa), P(lse), P(idx), P(ws), ws_bytes, nseq, k.shape[0], cache.ck.shape[0],
+                                         cache.max_tc, Hq, Hkv, D, module.compression_block, module.compression_stride,
                                          module.selection_block_size, n_sel, module.sliding_window, float(scale),
                                          _lib.stream()), "nsa_decode_fwd")
     if return_parts:
