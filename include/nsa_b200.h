@@ -81,15 +81,20 @@ int nsa_cmp_attn_fwd(const void* q, const void* ck, const void* cv, void* o, flo
                      float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride,
                      int causal, float scale, int n_sel, int pool_k, int pool_s, int pool_p, void* stream);
 int nsa_pool_out_len(int n, int pool_k, int pool_s, int pool_p);
-/* nsa_cmp_attn_fwd_sharded with the module's gate projection fused in: while the query tile is resident the kernel also
- * computes g_x[r] = q[r,:] . gate_w[x,:] + gate_b[x] for x = 0,1,2 = selected, window, compressed (gate_w [3,D] bf16,
- * gate_b [3] bf16 or NULL, no activation) and writes the three gates to g_slc, g_swa, g_cmp [B,Tq,Hq] bf16.
- * Replaces, in addition, self.gating = nn.Linear(head_dim, 3) applied at nsa/nsa.py:117.  Tq = T, q0 = 0 for an
- * unsharded call. */
+/* nsa_cmp_attn_fwd_sharded with two options.
+ * (1) gate_w != NULL: the module's gate projection fused in.  While the query tile is resident the kernel also computes
+ * g_x[r] = q[r,:] . gate_w[x,:] + gate_b[x] for x = 0,1,2 = selected, window, compressed (gate_w [3,D] bf16, gate_b [3]
+ * bf16 or NULL, no activation) and writes the three gates to g_slc, g_swa, g_cmp [B,Tq,Hq] bf16.  Replaces, in addition,
+ * self.gating = nn.Linear(head_dim, 3) applied at nsa/nsa.py:117.
+ * (2) score_mode: 0 = the reference's selection scores (soft-max of the UNSCALED, UNMASKED q.ck over ALL compressed keys,
+ * nsa/torch_attention.py:121-125, under which blocks in a query's future can be selected and are then skipped);
+ * 1 = causal scores: the compressed branch's own attention probabilities (scaled by `scale`, masked by t >= stride*j +
+ * block) summed over the group's heads and pooled, as in the NSA paper; needs causal = 1.  No counterpart in the
+ * reference.  Tq = T, q0 = 0 for an unsharded call. */
 int nsa_cmp_attn_fwd_gated(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
                            float* sel_scores, const void* gate_w, const void* gate_b, void* g_slc, void* g_swa, void* g_cmp,
                            int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal, float scale,
-                           int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream);
+                           int n_sel, int pool_k, int pool_s, int pool_p, int score_mode, int Tq, int q0, void* stream);
 /* Replaces _attention.backward (nsa/triton_attention.py:479-546).  dout [B,T,Hq,D]; delta [B,T,Hq] fp32 =
  * rowsum(o*dout) (times gate if gate != NULL); gate [B,T,Hq] or NULL scales dout per row.
  * dq [B,T,Hq,D] (added to when accumulate_dq); dck,dcv [B,Tc,Hk,D]. */

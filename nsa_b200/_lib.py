@@ -27,7 +27,7 @@ SIGNATURES = {
     "nsa_compress_bwd_noalloc": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "nsa_cmp_attn_fwd": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, P]),
     "nsa_pool_out_len": (I, [I, I, I, I]),
-    "nsa_cmp_attn_fwd_gated": (I, [P] * 12 + [I, I, I, I, I, I, I, I, I, F, I, I, I, I, I, I, P]),
+    "nsa_cmp_attn_fwd_gated": (I, [P] * 12 + [I, I, I, I, I, I, I, I, I, F, I, I, I, I, I, I, I, P]),
     "nsa_cmp_attn_bwd": (I, [P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I, I, F, P]),
     "nsa_cmp_attn_bwd_workspace_bytes": (Z, [I, I, I, I, I]),
     "nsa_sel_swa_fwd": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),

@@ -158,7 +158,7 @@ struct GateArgs {   // optional gate projection fused into the compressed-attent
 static int cmp_attn_fwd_impl(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
                      float* sel_scores, int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal,
                      float scale, int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream,
-                     const GateArgs* gate = nullptr) {
+                     const GateArgs* gate = nullptr, int score_mode = 0) {
   const bool sharded = (Tq != T) || (q0 != 0);
   if (Tq <= 0 || q0 < 0 || q0 + Tq > T) return fail(-12, "%s: query shard [%d, %d) is outside the sequence of %d tokens", "nsa_cmp_attn_fwd", q0, q0 + Tq, T);
   (void)sharded;
@@ -169,7 +169,9 @@ static int cmp_attn_fwd_impl(const void* q, const void* ck, const void* cv, void
   DenseArgs a = {};
   a.mode = 1; a.q = (const bf16*)q; a.k = (const bf16*)ck; a.v = (const bf16*)cv; a.o = (bf16*)o; a.lse = lse;
   a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = Tc; a.Hq = Hq; a.Hk = Hk; a.cblock = block; a.cstride = stride; a.causal = causal;
-  a.scale = scale; a.n_sel = n_sel;
+  a.scale = scale; a.n_sel = n_sel; a.score_mode = score_mode;
+  if (score_mode != 0 && score_mode != 1) return fail(-16, "nsa_cmp_attn_fwd: score_mode must be 0 (reference) or 1 (causal)");
+  if (score_mode == 1 && !causal) return fail(-16, "nsa_cmp_attn_fwd: causal selection scores need causal = 1");
   if (n_sel > 0) {
     if (!sel_idx) return fail(-1, "nsa_cmp_attn_fwd: sel_idx is null");
     if (Hq / Hk != 16)
@@ -187,6 +189,7 @@ static int cmp_attn_fwd_impl(const void* q, const void* ck, const void* cv, void
     return launch_dense_fwd2_tc(a, (cudaStream_t)stream);
   }
   if (sharded) return fail(-11, "query shards need head_dim 128 and the default pooling geometry");
+  if (score_mode == 1 && n_sel > 0) return fail(-16, "causal selection scores need head_dim 128 and the default pooling geometry");
   rc = launch_dense_fwd(a, D, (cudaStream_t)stream);
   if (rc || !gate) return rc;
   return launch_gate_fwd((const bf16*)q, (const bf16*)gate->w, (const bf16*)gate->b, (bf16*)gate->g[0], (bf16*)gate->g[1],
@@ -208,10 +211,10 @@ int nsa_cmp_attn_fwd_sharded(const void* q, const void* ck, const void* cv, void
 int nsa_cmp_attn_fwd_gated(const void* q, const void* ck, const void* cv, void* o, float* lse, int32_t* sel_idx,
                            float* sel_scores, const void* gate_w, const void* gate_b, void* g_slc, void* g_swa, void* g_cmp,
                            int B, int T, int Tc, int Hq, int Hk, int D, int block, int stride, int causal, float scale,
-                           int n_sel, int pool_k, int pool_s, int pool_p, int Tq, int q0, void* stream) {
-  if (!gate_w || !g_slc || !g_swa || !g_cmp) return fail(-1, "nsa_cmp_attn_fwd_gated: null gate weight or gate output");
+                           int n_sel, int pool_k, int pool_s, int pool_p, int score_mode, int Tq, int q0, void* stream) {
+  if (gate_w && (!g_slc || !g_swa || !g_cmp)) return fail(-1, "nsa_cmp_attn_fwd_gated: null gate output");
   const GateArgs g = {gate_w, gate_b, {g_slc, g_swa, g_cmp}};
-  return cmp_attn_fwd_impl(q, ck, cv, o, lse, sel_idx, sel_scores, B, T, Tc, Hq, Hk, D, block, stride, causal, scale, n_sel, pool_k, pool_s, pool_p, Tq, q0, stream, &g);
+  return cmp_attn_fwd_impl(q, ck, cv, o, lse, sel_idx, sel_scores, B, T, Tc, Hq, Hk, D, block, stride, causal, scale, n_sel, pool_k, pool_s, pool_p, Tq, q0, stream, gate_w ? &g : nullptr, score_mode);
 }
 
 size_t nsa_cmp_attn_bwd_workspace_bytes(int B, int T, int Tc, int Hk, int D) {

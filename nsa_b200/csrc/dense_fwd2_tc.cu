@@ -60,8 +60,13 @@ __device__ __forceinline__ Sched make_sched(const DenseArgs& a, int t0) {
     s.first = 0;
     s.nAttn = (nvis + 127) / 128;
     const bool sel = a.n_sel > 0;
-    s.nA = sel ? nt_all : s.nAttn;
-    s.nB = sel ? nt_all : 0;
+    if (sel && a.score_mode == 1) {   // causal scores: both passes stop at the last visible tile
+      s.nA = s.nAttn;
+      s.nB = s.nAttn;
+    } else {
+      s.nA = sel ? nt_all : s.nAttn;
+      s.nB = sel ? nt_all : 0;
+    }
   }
   return s;
 }
@@ -147,6 +152,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int ntile = (a.Tq + kTok - 1) / kTok;
   const long long total = (long long)a.B * HG * ntile;
   const bool do_sel = MODE == 1 && a.n_sel > 0;
+  const bool causal_scores = do_sel && a.score_mode == 1;
 
   if (warp == 0) {
     // ------------------------------- TMA producer ------------------------------------------------
@@ -400,8 +406,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int jt = sc.first + (passB ? i - sc.nA : i);
         const int j0 = jt * 128;                 // first key column of the tile
         if (do_sel && i == sc.nA) {
-          sel_m = m2;
-          sel_inv = l2 > 0.f ? 1.f / l2 : 0.f;
+          if (causal_scores) {   // the attention soft-max's own statistics (log2 domain, scaled scores)
+            sel_m = m_run > -INFINITY ? m_run : 0.f;
+            sel_inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          } else {
+            sel_m = m2;
+            sel_inv = l2 > 0.f ? 1.f / l2 : 0.f;
+          }
           named_bar_sync(1 + g, kGroup);         // the pool of this group has been cleared by all of its threads
         }
         ok = mbar_wait_abortable(s_full, cs & 1, 107, abort_flag) && ok;
@@ -418,16 +429,17 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc_fence_before();
           mbar_arrive(p_full);
         }
-        if (do_sel) {
-          // columns past Lk exist only in the last tile; rows past Tq contribute nothing to the scores
-          const int nval = min(128, a.Lk - j0);
+        if (do_sel && !(causal_scores && !passB)) {
+          // columns past Lk exist only in the last tile (reference scores); causal scores stop at the row's last
+          // visible key; rows past Tq contribute nothing to the scores
+          const int nval = min(128, (causal_scores ? nvis : a.Lk) - j0);
           if (nval < 128) {
 #pragma unroll
             for (int e = 0; e < 128; ++e)
               if (e >= nval) s[e] = -INFINITY;
           }
         }
-        if (do_sel && !passB) {
+        if (do_sel && !passB && !causal_scores) {
           // statistics of the raw-score soft-max over all compressed keys
           const float mnew = fmaxf(m2, max128(s));
           if (mnew > -INFINITY) {
@@ -448,7 +460,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           // p = softmax(raw) of this row; pool inside the thread (block k: columns 4k..4k+4; its fifth column is the
           // first column of block k+1), then sum the 16 heads of the token with a halving butterfly: after four
           // exchange steps every lane of the 16 holds two of the 32 sums.  Done per half of 64 columns.
-          const float nm = -sel_m * kLog2e;
+          const float cmul = causal_scores ? sl2 : kLog2e;
+          const float nm = causal_scores ? -sel_m : -sel_m * kLog2e;
           const float inv_b = live ? sel_inv : 0.f;
           float* pt = gpool + tl * pool_floats;
 #pragma unroll
@@ -459,7 +472,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int k = 0; k < 16; ++k) {
               float pe[4];
 #pragma unroll
-              for (int u = 0; u < 4; ++u) pe[u] = ex2(fmaf(s[hh * 64 + 4 * k + u], kLog2e, nm)) * inv_b;   // masked columns: 0
+              for (int u = 0; u < 4; ++u) pe[u] = ex2(fmaf(s[hh * 64 + 4 * k + u], cmul, nm)) * inv_b;   // masked columns: 0
               v[k] = (pe[0] + pe[1]) + (pe[2] + pe[3]);
               v[16 + k] = pe[0];
             }

@@ -59,6 +59,9 @@ struct DenseArgs {
   int causal;          // mode 1
   float scale;
   // mode 1 forward only: block selection fused behind the attention
+  int score_mode;      // selection scores: 0 = the reference's (soft-max of the UNSCALED, UNMASKED q.ck over all compressed
+                       // keys, nsa/torch_attention.py:121-125); 1 = causal: the compressed branch's own attention
+                       // probabilities (scaled, masked), so no block that starts in a query's future can be selected
   int n_sel;           // 0 = no selection
   int pool_k, pool_s, pool_p, n_pool;
   int* sel_idx;        // [B,T,Hq/16,n_sel] int32

@@ -22,6 +22,7 @@ class _NSACore(torch.autograd.Function):
         launches; slower than the streaming kernels at large shapes, see NSAAttention.fuse_row_passes)."""
         (stride, block, causal, scale, pool_k, pool_s, pool_p, n_sel, sel_block, window, q0) = cfg[:11]
         fused = len(cfg) > 11 and bool(cfg[11])
+        score_mode = int(cfg[12]) if len(cfg) > 12 else 0
         q, k, v, ck, cv = (_lib.require(t, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (ck, "ck"), (cv, "cv")))
         w_gate = _lib.require(w_gate, "gating.weight")
         b_gate = _lib.require(b_gate, "gating.bias") if b_gate is not None else None
@@ -42,14 +43,14 @@ class _NSACore(torch.autograd.Function):
             # compressed attention + block selection; the gate projection rides on the resident query tiles
             _lib.check(L.nsa_cmp_attn_fwd_gated(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, P(w_gate),
                                                 P(b_gate), P(g_slc), P(g_swa), P(g_cmp), B, T, Tc, Hq, Hkv, D, block, stride,
-                                                1 if causal else 0, scale, n_sel, pool_k, pool_s, pool_p, Tq, q0, S()),
-                       "nsa_cmp_attn_fwd_gated")
+                                                1 if causal else 0, scale, n_sel, pool_k, pool_s, pool_p, score_mode, Tq,
+                                                q0, S()), "nsa_cmp_attn_fwd_gated")
         else:
             _lib.check(L.nsa_gate_fwd(P(q), P(w_gate), P(b_gate), P(g_slc), P(g_swa), P(g_cmp), B * Tq * Hq, D, S()),
                        "nsa_gate_fwd")
-            _lib.check(L.nsa_cmp_attn_fwd_sharded(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, B, T, Tc, Hq, Hkv,
-                                                  D, block, stride, 1 if causal else 0, scale, n_sel, pool_k, pool_s,
-                                                  pool_p, Tq, q0, S()), "nsa_cmp_attn_fwd")
+            _lib.check(L.nsa_cmp_attn_fwd_gated(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, None, None, None,
+                                                None, None, B, T, Tc, Hq, Hkv, D, block, stride, 1 if causal else 0, scale,
+                                                n_sel, pool_k, pool_s, pool_p, score_mode, Tq, q0, S()), "nsa_cmp_attn_fwd")
         _lib.check(L.nsa_sel_swa_fwd_sharded(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(lse_slc), P(o_swa),
                                              P(lse_swa), P(g_slc), P(g_swa), P(o_cmp), P(g_cmp), P(o), B, T, Hq, Hkv, D,
                                              n_sel, sel_block, window, scale, Tq, q0, S()), "nsa_sel_swa_fwd")
@@ -164,6 +165,11 @@ class NSAAttention(nn.Module):
         # which pays for small, launch-bound shapes; at the benchmark's shape the separate streaming kernels are faster
         # (they read rows fully coalesced; a thread-per-row epilogue does not), so the default is False.
         self.fuse_row_passes = False
+        # Selection scores (also not a constructor argument).  "reference": what the reference's scoring does -- the
+        # soft-max of the unscaled, unmasked q.ck over all compressed keys (nsa/torch_attention.py:121-125), so blocks in
+        # a query's future can be selected and are then skipped.  "causal": the compressed branch's own attention
+        # probabilities (scaled, causally masked), as in the NSA paper: every selected block is visible.
+        self.score_mode = "reference"
 
     def forward(
         self,
@@ -204,7 +210,7 @@ class NSAAttention(nn.Module):
         v4 = v.reshape(bs, -1, num_kv_head, head_v_dim)
         cfg = (self.compression_stride, self.compression_block, bool(causal), float(scale), self.pool_kernel_size,
                self.pool_stride, self.pool_padding, self.selected_block_count, self.selection_block_size,
-               self.sliding_window, 0, self.fuse_row_passes)
+               self.sliding_window, 0, self.fuse_row_passes, {"reference": 0, "causal": 1}[self.score_mode])
         # the gate projection (nn.Linear(head_dim, 3), no activation) runs inside the fused node
         o = _NSACore.apply(q4, k4, v4, ck, cv, self.gating.weight, self.gating.bias, cfg)
         return o.reshape(-1, *o.shape[-2:])

@@ -119,6 +119,32 @@ def pooled_scores(q: torch.Tensor, ck: torch.Tensor, n_kv_head: int, kernel: int
     return out
 
 
+def pooled_scores_causal(q: torch.Tensor, ck: torch.Tensor, n_kv_head: int, kernel: int, stride: int, pad: int,
+                         cstride: int, cblock: int, scale: Optional[float] = None) -> torch.Tensor:
+    """Causal variant of the importance scores (no counterpart in the reference; the NSA paper's definition): the
+    compressed branch's own attention probabilities -- softmax of the SCALED scores over the compressed positions
+    visible to the query (t >= j*cstride + cblock; rows that see nothing score 0) -- summed over the query heads of
+    each KV group and pooled exactly as ``pooled_scores`` does.  Returns [B,Hkv,T,NB] fp32."""
+    B, T, Hq, D = q.shape
+    Tc, Hk = ck.shape[1], ck.shape[2]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    ckr = ck.float().repeat_interleave(Hq // Hk, dim=2) if Hk != Hq else ck.float()
+    s = torch.einsum("bthd,bshd->bhts", q.float(), ckr) * scale
+    masked = torch.arange(Tc).unsqueeze(0) * cstride + cblock > torch.arange(T).unsqueeze(1)
+    s = s.masked_fill(masked, float("-inf"))
+    ev = masked.all(-1).view(1, 1, T, 1)
+    p = torch.softmax(s.masked_fill(ev, 0.0), dim=-1).masked_fill(ev, 0.0).masked_fill(masked, 0.0)
+    p = p.reshape(B, n_kv_head, Hq // n_kv_head, T, Tc).sum(2)
+    nb = pool_out_len(Tc, kernel, stride, pad)
+    out = p.new_zeros(B, n_kv_head, T, nb)
+    for blk in range(nb):
+        lo = blk * stride - pad
+        hi = min(lo + kernel, Tc + pad)
+        out[..., blk] = p[..., max(lo, 0):min(hi, Tc)].sum(-1) / (hi - lo)
+    return out
+
+
 def topn_blocks(scores: torch.Tensor, n: int) -> torch.Tensor:
     """[B,Hkv,T,NB] -> [B,T,Hkv,n] int64; largest first, ties broken by the lower block index.
     (torch.topk at nsa/torch_attention.py:60 leaves the tie order unspecified; comparisons in

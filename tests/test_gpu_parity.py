@@ -248,6 +248,61 @@ def test_cmp_attention_fwd_bwd(nsa, D, Hq, Hkv, T, block, stride, causal):
     nsa._lib.device_status()
 
 
+def test_causal_score_mode(nsa):
+    """score_mode = causal: the selection scores are the compressed branch's own (scaled, masked) attention probabilities.
+    Pooled scores and the selected sets against the oracle's causal restatement; no selected block starts after the
+    query; the module's output with that selection against the oracle composition."""
+    from nsa_b200 import _lib
+    gen = torch.Generator().manual_seed(6)
+    B, T, Hq, Hkv, D, block, stride, n = 1, 2080, 32, 2, 128, 32, 16, 4
+    Tc = (T - block) // stride + 1
+    q = _r(torch.randn(B, T, Hq, D, generator=gen))
+    ck = _r(torch.randn(B, Tc, Hkv, D, generator=gen))
+    cv = _r(torch.randn(B, Tc, Hkv, D, generator=gen))
+    L, P, S = _lib.lib(), _lib.ptr, _lib.stream
+    n_pool = L.nsa_pool_out_len(Tc, 5, 4, 0)
+    qd, kd, vd = _dev(q), _dev(ck), _dev(cv)
+    o = torch.empty_like(qd)
+    lse = torch.empty(B, T, Hq, dtype=torch.float32, device=DEV)
+    idx = torch.empty(B, T, Hkv, n, dtype=torch.int32, device=DEV)
+    scores = torch.empty(B, Hkv, T, n_pool, dtype=torch.float32, device=DEV)
+    _lib.check(L.nsa_cmp_attn_fwd_gated(P(qd), P(kd), P(vd), P(o), P(lse), P(idx), P(scores), None, None, None, None, None,
+                                        B, T, Tc, Hq, Hkv, D, block, stride, 1, D ** -0.5, n, 5, 4, 0, 1, T, 0, S()),
+               "nsa_cmp_attn_fwd_gated")
+    ref = O.pooled_scores_causal(q, ck, Hkv, 5, 4, 0, stride, block)
+    _close("causal pooled scores", scores, ref, atol=2e-3, rtol=1e-2)
+    ro, _ = O.cmp_attention(q, ck, cv, stride, block, True)
+    _close("o_cmp (causal score mode)", o, ro)
+    # rows with fewer than n scored blocks pad with zero-score blocks (ties to the lower index); every block with a
+    # positive score starts at or before the query
+    hard, soft = O.index_sets_match(idx.cpu(), ref, n, gap=1e-3)
+    index_report("causal score mode T=%d" % T, hard, soft, idx.numel() // n)
+    assert hard == 0
+    sel_score = torch.gather(ref.permute(0, 2, 1, 3), -1, idx.cpu().long().clamp_min(0))
+    future = idx.cpu().long() * 64 > torch.arange(T).view(1, T, 1, 1)
+    assert not (future & (sel_score > 1e-3)).any(), "a block in the query's future was selected with a real score"
+    # the module with this mode: forward against the oracle composition on the kernel's own selection
+    mod, q2, k2, v2, _ = _module_and_oracle(nsa, 1, 1024, 32, 2, 128, 4, 128, seed=77)
+    mod.score_mode = "causal"
+    cu = torch.tensor([0, 1024], dtype=torch.int32, device=DEV)
+    q2d, k2d, v2d = (_dev(x.reshape(1024, -1, 128)) for x in (q2, k2, v2))
+    with torch.no_grad():
+        out = mod(q2d, k2d, v2d, cu, 1024)
+        ckd, cvd, _ = mod.compressor(k2d, v2d, cu, None)
+    sc2 = O.pooled_scores_causal(q2, ckd.float().cpu(), 2, 5, 4, 0, 16, 32)
+    idx2 = O.topn_blocks(sc2, 4)
+    wg, bg = mod.gating.weight.detach().float().cpu(), mod.gating.bias.detach().float().cpu()
+    o_cmp, _ = O.cmp_attention(q2, ckd.float().cpu(), cvd.float().cpu(), 16, 32, True)
+    o_slc, _ = O.selected_attention(q2, k2, v2, idx2, None, 64)
+    o_swa, _ = O.sliding_window_attention(q2, k2, v2, 128)
+    gate = _r(q2 @ wg.t() + bg)
+    ref2 = o_slc * gate[..., 0:1] + o_swa * gate[..., 1:2] + o_cmp * gate[..., 2:3]
+    # near-tie selections can differ from the oracle's top-n on a few rows: those rows are excluded, the rest must match
+    err = (out.view(1, 1024, 32, 128).float().cpu() - ref2).abs().amax((-1, -2))
+    assert float((err > 3e-2).float().mean()) < 0.02, "more than 2%% of the rows differ: %s" % err.topk(5).values
+    nsa._lib.device_status()
+
+
 def test_pooled_scores_dump_matches_oracle(nsa):
     """The fused score path (never written to HBM in production) can be dumped for inspection."""
     from nsa_b200 import _lib

@@ -113,3 +113,27 @@ def test_decode_row_equals_last_row_of_full_forward():
     full = O.nsa_forward(q, k, v, wk, bk, wv, bv, wg, bg, n_sel=3, window=64)
     row, _ = O.nsa_decode_row(q[0, -1], k[0], v[0], wk, bk, wv, bv, wg, bg, n_sel=3, window=64)
     _close(row, full[0, -1], 1e-4)
+
+
+def test_causal_scores_restatement_properties():
+    """pooled_scores_causal (no counterpart in the reference): only visible compressed positions carry weight, every
+    row's probabilities sum to the number of heads in the group, and the pooling is the same as pooled_scores'."""
+    import torch
+    from oracle import nsa_oracle as O
+    gen = torch.Generator().manual_seed(3)
+    B, T, Hq, Hkv, D, block, stride = 1, 320, 4, 2, 16, 32, 16
+    Tc = (T - block) // stride + 1
+    q, ck = torch.randn(B, T, Hq, D, generator=gen), torch.randn(B, Tc, Hkv, D, generator=gen)
+    sc = O.pooled_scores_causal(q, ck, Hkv, 5, 4, 0, stride, block)
+    nb = sc.shape[-1]
+    for t in (0, 31, 32, 100, 319):
+        nvis = 0 if t < block else min(Tc, (t - block) // stride + 1)
+        first_dead = (nvis + 3) // 4          # pooled block b covers positions 4b .. 4b+4
+        assert float(sc[0, :, t, first_dead:].abs().max()) == 0.0 if first_dead < nb else True
+    # un-pool: with kernel 5 / stride 4 position 4b is shared by blocks b-1 and b; check against a direct evaluation
+    s = torch.einsum("bthd,bshd->bhts", q, ck.repeat_interleave(Hq // Hkv, 2)) * D ** -0.5
+    masked = torch.arange(Tc).unsqueeze(0) * stride + block > torch.arange(T).unsqueeze(1)
+    p = torch.softmax(s.masked_fill(masked, float("-inf")), -1).nan_to_num(0.0)
+    p = p.reshape(B, Hkv, Hq // Hkv, T, Tc).sum(2)
+    direct = torch.stack([p[..., 4 * b:min(4 * b + 5, Tc)].sum(-1) / (min(4 * b + 5, Tc) - 4 * b) for b in range(nb)], -1)
+    assert torch.allclose(sc, direct, atol=1e-6)
