@@ -196,7 +196,7 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
     idx = torch.empty(B, T, Hkv, c["n_sel"], dtype=torch.int32, device=q4.device)
     dq, dk, dv = torch.empty_like(q4), torch.empty_like(k4), torch.empty_like(v4)
     dck, dcv = torch.empty_like(ck), torch.empty_like(cv)
-    ws1 = torch.empty(L.nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, c["n_sel"], c["sel_block"]), dtype=torch.uint8,
+    ws1 = torch.empty(_lib.sel_swa_bwd_workspace_bytes(B, T, T, Hq, Hkv, D, c["n_sel"], c["sel_block"]), dtype=torch.uint8,
                       device=q4.device)
     ws2 = torch.empty(L.nsa_cmp_attn_bwd_workspace_bytes(B, T, Tc, Hkv, D), dtype=torch.uint8, device=q4.device)
     P, S = _lib.ptr, _lib.stream

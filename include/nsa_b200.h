@@ -124,6 +124,13 @@ int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx
                     int accumulate_dq, void* dk, void* dv, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
                     int D, int S, int BS, int window, float scale, void* stream);
 size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS);
+/* The larger workspace with which nsa_sel_swa_bwd (and its _sharded / _fused forms; Tq = T when not sharded) takes the
+ * selected branch's dQ from the key-major dK/dV kernel: while a key block's dS tile is in shared memory that kernel also
+ * forms dS K for the visiting tokens and leaves one [16 heads x D] bf16 tile per (token, slot); a second kernel adds
+ * every token's S tiles in slot order (fixed order, no atomics).  This replaces the query-major dQ kernel, i.e. one of
+ * the two passes that recompute the selected branch's scores.  Extra bytes: B*Tq*Hkv*S*(4 + Hq/Hkv*D*2).  Used when
+ * D = 128, BS = 64 and dq, dk, dv are all requested; with the smaller workspace the query-major kernel runs. */
+size_t nsa_sel_swa_bwd_workspace_bytes_dq(int B, int T, int Tq, int Hq, int Hkv, int D, int S, int BS);
 
 /* Measurement aid, no counterpart in the reference: the K/V block gather of nsa_sel_swa_fwd's selected branch (same
  * items, same order, same TMA boxes of [BS keys x D]) with no arithmetic behind it, every SM keeping all of its shared

@@ -33,6 +33,7 @@ SIGNATURES = {
     "nsa_sel_swa_fwd": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),
     "nsa_sel_swa_bwd": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I, F, P]),
     "nsa_sel_swa_bwd_workspace_bytes": (Z, [I, I, I, I, I]),
+    "nsa_sel_swa_bwd_workspace_bytes_dq": (Z, [I, I, I, I, I, I, I, I]),
     "nsa_cmp_attn_fwd_sharded": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, I, I, P]),
     "nsa_cmp_attn_bwd_sharded": (I, [P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I, I, F, I, I, P]),
     "nsa_sel_swa_fwd_sharded": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P]),
@@ -82,6 +83,17 @@ def device_status():
     rc = lib().nsa_device_status()
     if rc != 0:
         raise RuntimeError("nsa_b200 device status %d: %s" % (rc, lib().nsa_last_error().decode()))
+
+
+# Selected-branch dQ from the key-major backward kernel (needs B*Tq*Hq*S*D*2 more bytes of workspace) or from the
+# query-major dQ kernel.  The library picks the path from the workspace size it is handed.
+SEL_DQ_FROM_KV = True
+
+
+def sel_swa_bwd_workspace_bytes(B, T, Tq, Hq, Hkv, D, S, BS):
+    if SEL_DQ_FROM_KV and D == 128 and BS == 64:
+        return lib().nsa_sel_swa_bwd_workspace_bytes_dq(B, T, Tq, Hq, Hkv, D, S, BS)
+    return lib().nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, S, BS)
 
 
 def ptr(t):

@@ -374,6 +374,13 @@ size_t nsa_sel_swa_bwd_workspace_bytes(int B, int T, int Hkv, int S, int BS) {
   return align_up(bh * NB * NB * 4, 256) + align_up(bh * (NB + 1) * 4, 256) + align_up(bh * (size_t)T * S * 4, 256);
 }
 
+// Extra workspace behind the reverse index for the selected branch's dQ as per-visit partials of the kv-major backward:
+// the inverse index [B,Tq,Hkv,S] int32 and one [16 x D] bf16 tile per (list position, 16-head sub-group).
+static size_t sel_dq_extra_bytes(int B, int Tq, int Hq, int Hkv, int D, int S) {
+  const size_t ent = (size_t)B * Tq * Hkv * S;
+  return align_up(ent * 4, 256) + align_up(ent * (size_t)(Hq / Hkv) * D * 2, 256);
+}
+
 struct PreSel {   // row pre-pass of the selected and window branches folded into the window's dQ kernel
   const void *o_slc, *o_swa;
   void *dg_slc, *dg_swa;
@@ -399,6 +406,11 @@ static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const v
   if (has_swa && (!lse_swa || !delta_swa)) return fail(-1, "nsa_sel_swa_bwd: window branch inputs missing");
   cudaStream_t s = (cudaStream_t)stream;
   const long long rows = (long long)B * Tq * Hq;
+  // With the larger workspace of nsa_sel_swa_bwd_workspace_bytes_dq the selected branch's dQ is produced by the
+  // kv-major backward (per-visit partial tiles + a slot-order reduction) instead of the query-major dQ kernel.
+  const bool dq_from_kv = dq && dk && has_slc && D == 128 && BS == 64 && S <= 32 && ws &&
+                          ws_bytes >= nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, S, BS) + sel_dq_extra_bytes(B, Tq, Hq, Hkv, D, S);
+  int dq_acc_for_reduce = accumulate_dq;
   bool fold = false;
   if (pre) {
     if ((has_slc && !pre->o_slc) || (has_swa && !pre->o_swa)) return fail(-1, "nsa_sel_swa_bwd_fused: a branch output is null");
@@ -438,7 +450,15 @@ static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const v
       if (rc) return rc;
       acc = 1;
     }
-    if (has_slc) {
+    if (has_slc && dq_from_kv) {
+      // nothing here: the reduction behind the kv-major kernel writes (or adds) the selected branch's dQ.  If the window
+      // kernel has not run yet it must not overwrite that: it runs now and the reduction accumulates.
+      if (has_swa && !fold) {
+        rc = run_swa();
+        if (rc) return rc;
+      }
+      dq_acc_for_reduce = (acc || has_swa) ? 1 : 0;
+    } else if (has_slc) {
       SelArgs a = {};
       a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64; a.counts = counts;
       a.lse = const_cast<float*>(lse_slc); a.dout = (const bf16*)dout_slc; a.delta = delta_slc;
@@ -448,7 +468,7 @@ static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const v
       if (rc) return rc;
       acc = 1;
     }
-    if (has_swa && !fold) {
+    if (has_swa && !fold && !(has_slc && dq_from_kv)) {
       rc = run_swa();
       if (rc) return rc;
     }
@@ -459,13 +479,13 @@ static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const v
     a.mode = 0; a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v;
     a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Lk = T; a.Hq = Hq; a.Hk = Hkv; a.BS = BS; a.window = has_swa ? window : 0; a.scale = scale;
     a.dk = (bf16*)dk; a.dv = (bf16*)dv;
+    RevArgs r = {};
     if (has_slc) {
       if (!ws || ws_bytes < nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, S, BS))
         return fail(-6, "nsa_sel_swa_bwd: workspace too small");
       const int NB = (T + BS - 1) / BS;
       const size_t bh = (size_t)B * Hkv;
       char* p = (char*)ws;
-      RevArgs r = {};
       r.idx = idx; r.idx64 = idx64; r.counts = counts; r.B = B; r.T = T; r.Tq = Tq; r.q0 = q0; r.H = Hkv; r.S = S; r.BS = BS; r.NB = NB;
       r.hist = (int*)p;
       p += align_up(bh * NB * NB * 4, 256);
@@ -473,6 +493,12 @@ static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const v
       p += align_up(bh * (NB + 1) * 4, 256);
       r.rev_tok = (int*)p;
       r.cap = (long long)Tq * S;
+      if (dq_from_kv) {
+        p += align_up(bh * (size_t)T * S * 4, 256);
+        r.inv = (int*)p;
+        p += align_up((size_t)B * Tq * Hkv * S * 4, 256);
+        a.dq_part = (bf16*)p;
+      }
       rc = launch_build_rev(r, s);
       if (rc) return rc;
       a.rev_ptr = r.rev_ptr; a.rev_tok = r.rev_tok; a.rev_cap = r.cap;
@@ -484,8 +510,16 @@ static int sel_swa_bwd_impl(const void* q, const void* k, const void* v, const v
     if (!(D == 128 && BS == 64) && sharded) return fail(-11, "query shards need head_dim 128 and 64-key selection blocks");
     rc = (D == 128 && BS == 64) ? launch_kv_bwd_tc(a, s) : launch_kv_bwd(a, D, s);
     if (rc) return rc;
+    if (dq_from_kv) {   // every token's partial tiles, in slot order, onto dq (after the window's dQ if that ran first)
+      rc = launch_sel_dq_reduce(r, a.dq_part, (bf16*)dq, Hq, D, scale, dq_acc_for_reduce, s);
+      if (rc) return rc;
+    }
   }
   return 0;
+}
+
+size_t nsa_sel_swa_bwd_workspace_bytes_dq(int B, int T, int Tq, int Hq, int Hkv, int D, int S, int BS) {
+  return nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, S, BS) + sel_dq_extra_bytes(B, Tq, Hq, Hkv, D, S);
 }
 
 int nsa_sel_swa_bwd(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,

@@ -104,6 +104,8 @@ struct KvArgs {
   long long rev_cap;
   bf16* dk;               // [B,Lk,Hk,D]
   bf16* dv;
+  bf16* dq_part;          // mode 0, optional: the selected branch's dQ as per-visit partial tiles [B,Hk,rev_cap,G16][16][D]
+                          // (position = place in the reverse-index list), summed later by launch_sel_dq_reduce
   float* part;            // mode 1 workspace: [2][nseg][B,Lk,Hk,D] fp32
   int nseg, seg_len;
   int B, T, Lk, Hq, Hk, BS, window;
@@ -203,8 +205,14 @@ struct RevArgs {
   int* rev_tok;   // [B,H,cap]
   long long cap;  // Tq*S
   int Tq, q0;     // query shard: idx/counts hold Tq rows per batch; T is the key sequence length
+  int* inv;       // optional [B,Tq,H,S]: for every valid (row, slot) its position in the (b,h) list of rev_tok
 };
 int launch_build_rev(const RevArgs& a, cudaStream_t s);
+// dq[(b,t), 16-head group] (+)= scale * sum over the valid slots s of part[(b,h) list position inv[row,s]] (fixed slot
+// order).  part holds one [16 heads x D] bf16 tile per (list position, 16-head sub-group), written by the kv-major
+// backward; dq rows of a (token, group) are the same contiguous tile.
+int launch_sel_dq_reduce(const RevArgs& a, const bf16* part, bf16* dq, int Hq, int D, float scale, int accumulate,
+                         cudaStream_t s);
 // out(bf16)[i] = sum over valid segments of part[seg][i]
 int launch_reduce_segments(const float* part, bf16* out, int nseg, long long n_per_seg, int q0, int Tq, int Lk, int Hk,
                            int D, int seg_len, int cblock, int cstride, int causal, cudaStream_t s);

@@ -14,6 +14,11 @@
 // from TMEM, form P and dS = P (g dP - delta), and store both as bf16 tiles.
 // The MMA thread issues S/dP of batch n+1 before dV/dK of batch n, so the tensor core works while the soft-max
 // warps compute.  dV^T and dK^T stay in TMEM for the CTA's whole token stream and are stored once.
+// Optionally (mode 0) the selected branch's dQ comes out of this kernel too: dS of a batch is already in shared memory,
+// so one more product  dQ_part[128 rows x 128 d] = dS . K  (A = dS K-major, B = K MN-major, a third accumulator in TMEM)
+// gives the batch's contribution to dQ, which the soft-max warps store as bf16 tiles indexed by the batch's positions
+// in the reverse-index list; a small kernel later sums every token's tiles in slot order.  That replaces the
+// query-major dQ kernel, which gathers every selected block again (32 KB per visit for 16 rows) and recomputes S and dP.
 // Every wait is bounded; on a time-out the role records an error and leaves its loop.
 #include "kernels.h"
 #include "tc.cuh"
@@ -40,7 +45,7 @@ constexpr uint32_t P_TILE = 128 * 128;     // [128 rows][64 keys]
 constexpr int kStages = 2;
 constexpr uint32_t kSmem = 2 * KV_TILE + kStages * STAGE + 4 * P_TILE + 256 + 1024;
 constexpr uint32_t kTmemCols = 512;        // two S/dP buffers: S 0..63, dP 64..127 | 128..255; dV^T 256..319, dK^T 320..383
-constexpr uint32_t kColDV = 256, kColDK = 320;
+constexpr uint32_t kColDV = 256, kColDK = 320, kColDQ = 384;   // dQ_part: 384..511
 
 struct Stream {  // the token stream of one CTA: branch A (list or range) then branch B (window range)
   int nA, nB, ta_lo, tb_lo;
@@ -60,7 +65,8 @@ template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
     kv_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDOa,
                      const __grid_constant__ CUtensorMap tmDOb, const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const KvArgs a) {
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQw,
+                     const __grid_constant__ CUtensorMap tmDOw, const KvArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sbase = (raw + 1023u) & ~1023u;
@@ -75,7 +81,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // hold batch n, and P/dS of batch n+1 are written while dV/dK of batch n still read theirs
   const uint32_t full0 = bar_base, empty0 = bar_base + 16, kv_bar = bar_base + 32, sdp_full = bar_base + 40,
                  sdp_free = bar_base + 56, pds_full = bar_base + 72, pds_free = bar_base + 88, acc_full = bar_base + 104,
-                 tmem_slot = bar_base + 112;
+                 tmem_slot = bar_base + 112, dq_full = bar_base + 120, dq_free = bar_base + 128;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(full0 + 8 * i, kProd);
@@ -89,6 +95,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(pds_free + 8 * i, 1);
     }
     mbar_init(acc_full, 1);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, kSoftThreads);
     fence_mbar_init();
   }
   if (warp == kMmaWarp) tmem_alloc(tmem_slot, kTmemCols);
@@ -141,12 +149,15 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int nbA = (st.nA + kTokB - 1) / kTokB, nbB = (st.nB + kTokB - 1) / kTokB;
   const int nb_sub = nbA + nbB;             // batches per 16-head sub-group
   const int nb = skip ? 0 : nb_sub * G16;   // batches of this CTA
+  const bool emit_dq = MODE == 0 && a.dq_part != nullptr;   // selected-branch batches also leave their dQ partial
 
   if (!skip && warp < kProd) {
     // ------------------------------- TMA producers -----------------------------------------------
-    // A batch is 32 boxes of 2 KB: (token j, Q or dO, column panel).  Box x = 3 * lane + warp belongs to this lane;
-    // every producer warp issues its 10 or 11 boxes with a single instruction and arms the stage's barrier with
-    // their byte count.  Token ids are fetched one batch ahead.
+    // A batch of gathered tokens (a reverse-index list) is 32 boxes of 2 KB: (token j, Q or dO, column panel).  Box
+    // x = 3 * lane + warp belongs to this lane; every producer warp issues its 10 or 11 boxes with a single instruction
+    // and arms the stage's barrier with their byte count.  Token ids are fetched one batch ahead.
+    // A batch of consecutive tokens (the window's range, the compressed branch's range) is 4 boxes of 16 KB instead:
+    // [64 columns x 16 heads x 8 tokens] through the 4-D maps, rows past the last token read as zero.
     if (warp == 0 && lane == 0) {
       mbar_expect_tx(kv_bar, 2 * KV_TILE);
 #pragma unroll
@@ -159,6 +170,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool has = x < 4 * kTokB;
     const int bj = x & 7, bwhich = (x >> 3) & 1, bp = x >> 4;
     const int nmine = (4 * kTokB - warp + kProd - 1) / kProd;   // boxes this warp issues per batch
+    const bool has_w = x < 4;                                   // this lane's 16 KB box of a consecutive-token batch
+    const int nmine_w = (4 - warp + kProd - 1) / kProd;
     auto batch_token = [&](int n) {
       if (n >= nb || !has) return 0;
       const int m = n % nb_sub;
@@ -173,16 +186,24 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int br = m < nbA ? 0 : 1;
       const int hg = hk * G16 + sub;
       const CUtensorMap* tmDO = br == 0 ? &tmDOa : &tmDOb;
+      const bool contig = br == 1 || st.list == nullptr;
       const int stage = n % kStages;
       const uint32_t ph = (n / kStages) & 1;
       const uint32_t fb = full0 + 8 * stage;
       int good = 1;
       if (lane == 0) {
         good = mbar_wait(empty0 + 8 * stage, ph ^ 1, DEV_ERR_EMPTY_WAIT) ? 1 : 0;
-        if (good) mbar_expect_tx(fb, nmine * 2048);
+        if (good) mbar_expect_tx(fb, contig ? nmine_w * 16384 : nmine * 2048);
       }
       if (!__shfl_sync(0xffffffffu, good, 0)) break;
-      if (has) {
+      if (contig) {
+        if (has_w) {
+          const uint32_t q_s = ring + stage * STAGE, do_s = q_s + Q_TILE;
+          const int t0 = (br == 0 ? st.ta_lo + m * kTokB : st.tb_lo + (m - nbA) * kTokB) - a.q0;
+          const int wh = x >> 1, pp = x & 1;
+          tma_load_4d((wh ? do_s : q_s) + pp * Q_PANEL, wh ? &tmDOw : &tmQw, fb, pp * 64, hg * 16, t0, b);
+        }
+      } else if (has) {
         const uint32_t q_s = ring + stage * STAGE, do_s = q_s + Q_TILE;
         const int qrow = (int)(((long long)b * a.Tq + (tk - a.q0)) * a.Hq + hg * 16);
         tma_load_2d((bwhich ? do_s : q_s) + bp * Q_PANEL + bj * 2048, bwhich ? tmDO : &tmQ, fb, bp * 64, qrow);
@@ -225,6 +246,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         umma_commit(sdp_full + 8 * (n & 1));
       };
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, 0, 1);  // A = dS K-major, B = K MN-major
+      const uint64_t dKmn = umma_smem_desc(k_s, KV_PANEL, 1024);
+      uint64_t dDSk[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) dDSk[i] = umma_smem_desc(p_s0 + i * 2 * P_TILE + P_TILE, 0, 1024);
+      int ndq = 0;   // dQ partials issued so far
       auto issue_dkv = [&](int n) {
         const uint64_t aq = (n % kStages) ? dQmn[1] : dQmn[0], ado = (n % kStages) ? dDOmn[1] : dDOmn[0];
         const uint64_t bp = (n & 1) ? dP[1] : dP[0], bds = (n & 1) ? dDS[1] : dDS[0];
@@ -235,6 +262,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int ks = 0; ks < 8; ++ks)
           umma_ss(tmem + kColDK, umma_desc_advance(aq, ks * 2048), umma_desc_advance(bds, ks * 2048), idesc_mn, (n | ks) ? 1u : 0u);
         umma_commit(empty0 + 8 * (n % kStages));
+        if (emit_dq && (n % nb_sub) < nbA) {
+          // the previous partial must have been read out of its accumulator (the soft-max warps do that right after
+          // handing over this batch's P/dS, so the wait is short and dV/dK above are already running)
+          if (ndq > 0) ok = ok && mbar_wait(dq_free, (ndq - 1) & 1, DEV_ERR_EMPTY_WAIT);
+          tc_fence_after();
+          const uint64_t ads = (n & 1) ? dDSk[1] : dDSk[0];
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)   // contraction over the 64 keys, 16 per step
+            umma_ss(tmem + kColDQ, umma_desc_advance(ads, ks * 32), umma_desc_advance(dKmn, ks * 2048), idesc_dq, ks ? 1u : 0u);
+          umma_commit(dq_full);
+          ++ndq;
+        }
         umma_commit(pds_free + 8 * (n & 1));
       };
       // Event loop: S/dP of batch `ns` is issued as soon as its Q/dO stage has landed and its TMEM buffer is free,
@@ -314,6 +353,35 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (gp) r.gv = __bfloat162float(gp[qrow]);
       }
       return r;
+    };
+    // dQ partial of batch m (a selected-branch batch): this thread's half row -> the tile of its list position
+    int ndq = 0;
+    auto drain_dq = [&](int m_batch) {
+      ok = ok && mbar_wait(dq_full, ndq & 1, DEV_ERR_FULL_WAIT);
+      tc_fence_after();
+      const int sub = m_batch / nb_sub, mloc = m_batch % nb_sub;
+      const int i = mloc * kTokB + j;
+      uint4 outv[8];
+      __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(outv);
+      {
+        float vals[4][16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld16(tmem + lane_addr + kColDQ + half * 64 + c * 16, vals[c]);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(dq_free);   // the accumulator is in registers: the next partial may be issued
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ho[c * 8 + e] = __floats2bfloat162_rn(vals[c][2 * e], vals[c][2 * e + 1]);
+      }
+      if (ok && i < st.nA) {
+        const long long bh = (long long)b * a.Hk + hk;
+        bf16* dst = a.dq_part + (((bh * a.rev_cap + st.ta_lo + i) * G16 + sub) * 16 + head) * D + half * 64;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) reinterpret_cast<uint4*>(dst)[e] = outv[e];
+      }
+      ++ndq;
     };
     int br1, br2;
     bool live1, live2;
@@ -397,7 +465,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       fence_proxy_async();
       mbar_arrive(pds_full + 8 * buf);
+      // the previous batch's dQ partial is complete by now (its MMAs were issued a whole batch ago)
+      if (emit_dq && n > 0 && ((n - 1) % nb_sub) < nbA) drain_dq(n - 1);
     }
+    if (emit_dq && ok && nb > 0 && ((nb - 1) % nb_sub) < nbA) drain_dq(nb - 1);
     // ---- epilogue: dV^T / dK^T [d lanes x 64 key columns] -> global ---------------------------------------
     if (ok && nb > 0) ok = mbar_wait(acc_full, 0, DEV_ERR_FULL_WAIT);
     tc_fence_after();
@@ -437,7 +508,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 template <int MODE>
 int launch(const KvArgs& a, cudaStream_t s) {
-  CUtensorMap tmQ, tmA, tmB, tmK, tmV;
+  CUtensorMap tmQ, tmA, tmB, tmK, tmV, tmQw, tmDOw;
   const long long qrows = (long long)a.B * a.Tq * a.Hq;
   if (qrows > 0x7fffffffLL) {
     set_error("B*T*Hq exceeds the 2^31 rows a TMA coordinate can address");
@@ -448,6 +519,16 @@ int launch(const KvArgs& a, cudaStream_t s) {
   if (!rc) rc = make_tmap_rows2d(&tmB, a.dout_b ? a.dout_b : a.dout_a, D, qrows, 16);
   if (!rc) rc = make_tmap_rows4d(&tmK, a.k, D, a.Hk, a.Lk, a.B, 64);
   if (!rc) rc = make_tmap_rows4d(&tmV, a.v, D, a.Hk, a.Lk, a.B, 64);
+  {   // consecutive-token batches: [64 columns x 16 heads x 8 tokens] boxes of q and of that stream's dO
+    const unsigned long long dims[4] = {(unsigned long long)D, (unsigned long long)a.Hq, (unsigned long long)a.Tq,
+                                        (unsigned long long)a.B};
+    const unsigned long long strides[3] = {(unsigned long long)D * 2, (unsigned long long)a.Hq * D * 2,
+                                           (unsigned long long)a.Tq * a.Hq * D * 2};
+    const unsigned box[4] = {64, 16, (unsigned)kTokB, 1};
+    const void* dow = MODE == 0 ? (a.dout_b ? a.dout_b : a.dout_a) : a.dout_a;
+    if (!rc) rc = make_tmap_generic(&tmQw, a.q, 4, dims, strides, box);
+    if (!rc) rc = make_tmap_generic(&tmDOw, dow, 4, dims, strides, box);
+  }
   if (rc) return rc;
   auto kern = kv_bwd_tc_kernel<MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
@@ -462,7 +543,7 @@ int launch(const KvArgs& a, cudaStream_t s) {
     set_error("kv backward: grid too large");
     return -33;
   }
-  kern<<<(unsigned)grid, kThreads, kSmem, s>>>(tmQ, tmA, tmB, tmK, tmV, a);
+  kern<<<(unsigned)grid, kThreads, kSmem, s>>>(tmQ, tmA, tmB, tmK, tmV, tmQw, tmDOw, a);
   note_launches(1);
   return (int)cudaGetLastError();
 }

@@ -164,7 +164,10 @@ __global__ void rev_fill_kernel(const RevArgs a) {
       if (blk >= 0) {
         const int rank = __popc(same & ((1u << lane) - 1));
         const int pos = cur[blk] + rank;
-        if (pos < a.cap) out[pos] = t;
+        if (pos < a.cap) {
+          out[pos] = t;
+          if (a.inv) a.inv[row * a.S + s] = pos;
+        }
       }
       __syncwarp();
       if (blk >= 0 && (lane == 31 || (same >> (lane + 1)) == 0)) cur[blk] += __popc(same);  // highest lane of the group
@@ -220,6 +223,111 @@ int launch_combine(const bf16* a0, const bf16* g0, const bf16* a1, const bf16* g
   }
   const long long n8 = rows * (D / 8);
   combine_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, s>>>(a0, g0, a1, g1, a2, g2, o, n8, D / 8);
+  note_launches(1);
+  return (int)cudaGetLastError();
+}
+
+// Two warps per (batch, token, 16-head group), each half of the [16 x D] bf16 tile (heads 0-7 / 8-15): the token's
+// visits are added in slot order.  A load instruction of the warp covers 512 contiguous bytes; the list positions of
+// all slots are fetched first so that the tiles of several slots are in flight at once.
+template <int D>
+__global__ void __launch_bounds__(256) sel_dq_reduce_kernel(const RevArgs a, const bf16* __restrict__ part, bf16* __restrict__ dq,
+                                                            const int G16, const float scale, const int accumulate) {
+  const long long w2 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const long long total = (long long)a.B * a.Tq * a.H * G16;
+  const long long w = w2 >> 1;
+  if (w >= total) return;
+  const int hb = (int)(w2 & 1);                        // which half of the tile
+  const int lane = threadIdx.x & 31;
+  const int sub = (int)(w % G16);
+  const long long row = w / G16;                       // (b, tl, h) row of idx / counts
+  const int h = (int)(row % a.H);
+  const long long bt = row / a.H;
+  const int tl = (int)(bt % a.Tq), b = (int)(bt / a.Tq);
+  const int t = a.q0 + tl;
+  constexpr int NV = 8 * D / 8 / 32;                   // 16-byte vectors per lane: 4 at D = 128
+  float acc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[i][k] = 0.f;
+  const long long bh = (long long)b * a.H + h;
+  // lane s holds the list position of slot s (or -1): the same validity rule that built the lists
+  int mypos = -1;
+  if (lane < a.S && rev_block(a, row, lane, t) >= 0) mypos = a.inv[row * a.S + lane];
+  unsigned live = __ballot_sync(0xffffffffu, mypos >= 0);
+  const uint4* base = reinterpret_cast<const uint4*>(part) + hb * (8 * D / 8) + lane;
+  auto tile = [&](int s) {
+    const long long pos = __shfl_sync(0xffffffffu, mypos, s);
+    return base + ((bh * a.cap + pos) * G16 + sub) * (16 * D / 8);
+  };
+  auto add = [&](const uint4 (&v)[NV]) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(hv[k]);
+        acc[i][2 * k] += f.x;
+        acc[i][2 * k + 1] += f.y;
+      }
+    }
+  };
+  while (live) {
+    const int s0 = __ffs(live) - 1;
+    live &= live - 1;
+    const int s1 = live ? __ffs(live) - 1 : -1;
+    if (s1 >= 0) live &= live - 1;
+    const uint4* p0 = tile(s0);
+    const uint4* p1 = tile(s1 >= 0 ? s1 : s0);
+    uint4 v0[NV], v1[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v0[i] = __ldcs(p0 + 32 * i);
+    if (s1 >= 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) v1[i] = __ldcs(p1 + 32 * i);
+    }
+    add(v0);
+    if (s1 >= 0) add(v1);
+  }
+  const int Hq = a.H * G16 * 16;
+  uint4* dst = reinterpret_cast<uint4*>(dq + ((bt * Hq) + (long long)(h * G16 + sub) * 16) * D) + hb * (8 * D / 8) + lane;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float prev[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (accumulate) {
+      const uint4 v = dst[32 * i];
+      const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(hv[k]);
+        prev[2 * k] = f.x;
+        prev[2 * k + 1] = f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      ho[k] = __floats2bfloat162_rn(fmaf(acc[i][2 * k], scale, prev[2 * k]), fmaf(acc[i][2 * k + 1], scale, prev[2 * k + 1]));
+    dst[32 * i] = o;
+  }
+}
+
+int launch_sel_dq_reduce(const RevArgs& a, const bf16* part, bf16* dq, int Hq, int D, float scale, int accumulate,
+                         cudaStream_t s) {
+  if (D != 128) {
+    set_error("selected dQ reduction: head_dim 128 only");
+    return -2;
+  }
+  const int G16 = Hq / a.H / 16;
+  const long long total = (long long)a.B * a.Tq * a.H * G16;
+  if (total <= 0) return 0;
+  if (a.S > 32) {
+    set_error("selected dQ reduction: at most 32 selected blocks per token");
+    return -2;
+  }
+  sel_dq_reduce_kernel<128><<<(unsigned)((2 * total + 7) / 8), 256, 0, s>>>(a, part, dq, G16, scale, accumulate);
   note_launches(1);
   return (int)cudaGetLastError();
 }

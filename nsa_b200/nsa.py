@@ -80,7 +80,7 @@ class _NSACore(torch.autograd.Function):
             dg_swa.zero_()
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dck, dcv = torch.empty_like(ck), torch.empty_like(cv)
-        ws_bytes = L.nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, n_sel, sel_block)
+        ws_bytes = _lib.sel_swa_bwd_workspace_bytes(B, T, Tq, Hq, Hkv, D, n_sel, sel_block)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         ws2_bytes = L.nsa_cmp_attn_bwd_workspace_bytes(B, T, Tc, Hkv, D)
         ws2 = torch.empty(ws2_bytes, dtype=torch.uint8, device=dev)

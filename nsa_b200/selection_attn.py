@@ -85,7 +85,7 @@ class ParallelNSAFunction(torch.autograd.Function):
         opt = lambda t, sl: P(t[:, sl]) if t is not None else None
         for a, b in (seqs or [(0, T)]):
             sl = slice(a, b)
-            ws_bytes = L.nsa_sel_swa_bwd_workspace_bytes(B, b - a, Hkv, S, block_size)
+            ws_bytes = _lib.sel_swa_bwd_workspace_bytes(B, b - a, b - a, Hq, Hkv, D, S, block_size)
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
             _lib.check(L.nsa_sel_swa_bwd(
                 P(q[:, sl]), P(k[:, sl]), P(v[:, sl]), P(idx[:, sl]), i64, opt(counts, sl),
