@@ -241,6 +241,13 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
             P(q4), P(k4), P(v4), P(idx), 0, None, P(do4), P(lse_slc), P(delta), None, P(do4), P(lse_swa), P(delta), None,
             None, 0, P(dk), P(dv), P(ws1), ws1.numel(), B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"], c["window"], scale,
             S()),
+        # the call the module makes: window dQ, then the key-major kernel (dK, dV and the selected branch's dQ partials)
+        # and the reduction of the partials (large workspace); the query-major "sel_dq" above is what runs instead when
+        # a caller hands over only the small workspace
+        "sel+swa_bwd(all)": lambda: L.nsa_sel_swa_bwd(
+            P(q4), P(k4), P(v4), P(idx), 0, None, P(do4), P(lse_slc), P(delta), None, P(do4), P(lse_swa), P(delta), None,
+            P(dq), 0, P(dk), P(dv), P(ws1), ws1.numel(), B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"], c["window"], scale,
+            S()),
         "cmp_dq": lambda: L.nsa_cmp_attn_bwd(P(q4), P(ck), P(cv), P(lse_cmp), P(do4), P(delta), None, P(dq), 0, None, None,
                                              None, 0, B, T, Tc, Hq, Hkv, D, c["block"], c["stride"], 1, scale, S()),
         "cmp_dkv(+reduce)": lambda: L.nsa_cmp_attn_bwd(P(q4), P(ck), P(cv), P(lse_cmp), P(do4), P(delta), None, None, 0,
@@ -263,6 +270,8 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
         e1.record()
         torch.cuda.synchronize()
         out[name] = e0.elapsed_time(e1) / reps
+    # derived: the composite call minus the window dQ kernel timed alone
+    out["sel+swa_dkv+sel_dq(+reverse index,+reduce)"] = out["sel+swa_bwd(all)"] - out["swa_dq"]
     t = torch.arange(T, device=q4.device).view(1, T, 1, 1)
     valid = (idx >= 0) & (idx.long() * c["sel_block"] <= t)
     pairs = int(valid.sum().item())               # (token, kv head, block) visits
@@ -454,13 +463,17 @@ def run_gpu(args):
             "sel_fwd": fm_loc["slc"], "swa_fwd": fm_loc["swa"], "cmp_attn_fwd+select": fm_loc["cmp"],
             "sel_dq": fm_loc["slc"], "swa_dq": fm_loc["swa"], "cmp_dq": fm_loc["cmp"],
             "sel+swa_dkv(+reverse index)": 1.5 * (fm_loc["slc"] + fm_loc["swa"]), "cmp_dkv(+reduce)": 1.5 * fm_loc["cmp"],
+            # the whole 10D of the selected branch (S, dP, dV, dK, dQ) and the window's 6D in one pass over the keys
+            "sel+swa_dkv+sel_dq(+reverse index,+reduce)": 2.5 * fm_loc["slc"] + 1.5 * fm_loc["swa"],
             "compress_fwd(one of k,v)": fm_loc["comp"] / 2, "compress_bwd(one of k,v)": fm_loc["comp"],
         }
         # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels that can dominate, from
         # one ncu capture of the B=1 slice of this workload (`--profile-case`), in MB per sequence; traffic grows in
         # proportion to the number of sequences (every sequence's K/V stays in L2, q/dO/o/dq are streamed once).
         # NCU_TRAFFIC_COMMIT names the build the capture was taken from: a kernel changed since then has a stale entry.
-        dom = max((n for n in kern if n in kflops), key=lambda n: kern[n])
+        # not part of the module's step with the large workspace: the query-major selected dQ and the dK/dV-only call
+        not_in_step = ("sel_dq", "sel+swa_dkv(+reverse index)")
+        dom = max((n for n in kern if n in kflops and n not in not_in_step), key=lambda n: kern[n])
         # kernels timed alone (three launches back to back): the burst bf16 peak is their denominator
         peak = peaks["tf_burst"]
         kroof = {}

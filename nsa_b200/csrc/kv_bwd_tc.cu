@@ -234,14 +234,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       auto issue_sdp = [&](int n) {
         const uint64_t aq = (n % kStages) ? dQk[1] : dQk[0], ado = (n % kStages) ? dDOk[1] : dDOk[0];
         const uint32_t col = (n & 1) * 128;
+        // S and dP alternate: two MMAs in a row never accumulate into the same columns
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t aoff = (ks >> 2) * Q_PANEL + (ks & 3) * 32, boff = (ks >> 2) * KV_PANEL + (ks & 3) * 32;
           umma_ss(tmem + col, umma_desc_advance(aq, aoff), umma_desc_advance(dK, boff), idesc_kk, ks ? 1u : 0u);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t aoff = (ks >> 2) * Q_PANEL + (ks & 3) * 32, boff = (ks >> 2) * KV_PANEL + (ks & 3) * 32;
           umma_ss(tmem + col + 64, umma_desc_advance(ado, aoff), umma_desc_advance(dV, boff), idesc_kk, ks ? 1u : 0u);
         }
         umma_commit(sdp_full + 8 * (n & 1));
@@ -251,39 +248,47 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint64_t dDSk[2];
 #pragma unroll
       for (int i = 0; i < 2; ++i) dDSk[i] = umma_smem_desc(p_s0 + i * 2 * P_TILE + P_TILE, 0, 1024);
-      int ndq = 0;   // dQ partials issued so far
+      int ndq = 0;          // dQ partials issued so far
+      int dq_pending = -1;  // batch whose dQ partial waits for the accumulator to be drained
       auto issue_dkv = [&](int n) {
         const uint64_t aq = (n % kStages) ? dQmn[1] : dQmn[0], ado = (n % kStages) ? dDOmn[1] : dDOmn[0];
         const uint64_t bp = (n & 1) ? dP[1] : dP[0], bds = (n & 1) ? dDS[1] : dDS[0];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)   // contraction over the 128 rows, 16 per step
+        for (int ks = 0; ks < 8; ++ks) {  // contraction over the 128 rows, 16 per step; dV and dK alternate
           umma_ss(tmem + kColDV, umma_desc_advance(ado, ks * 2048), umma_desc_advance(bp, ks * 2048), idesc_mn, (n | ks) ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
           umma_ss(tmem + kColDK, umma_desc_advance(aq, ks * 2048), umma_desc_advance(bds, ks * 2048), idesc_mn, (n | ks) ? 1u : 0u);
-        umma_commit(empty0 + 8 * (n % kStages));
-        if (emit_dq && (n % nb_sub) < nbA) {
-          // the previous partial must have been read out of its accumulator (the soft-max warps do that right after
-          // handing over this batch's P/dS, so the wait is short and dV/dK above are already running)
-          if (ndq > 0) ok = ok && mbar_wait(dq_free, (ndq - 1) & 1, DEV_ERR_EMPTY_WAIT);
-          tc_fence_after();
-          const uint64_t ads = (n & 1) ? dDSk[1] : dDSk[0];
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)   // contraction over the 64 keys, 16 per step
-            umma_ss(tmem + kColDQ, umma_desc_advance(ads, ks * 32), umma_desc_advance(dKmn, ks * 2048), idesc_dq, ks ? 1u : 0u);
-          umma_commit(dq_full);
-          ++ndq;
         }
-        umma_commit(pds_free + 8 * (n & 1));
+        umma_commit(empty0 + 8 * (n % kStages));
+        if (emit_dq && (n % nb_sub) < nbA)
+          dq_pending = n;                  // its dS tile stays in use until the partial has been issued
+        else
+          umma_commit(pds_free + 8 * (n & 1));
       };
-      // Event loop: S/dP of batch `ns` is issued as soon as its Q/dO stage has landed and its TMEM buffer is free,
-      // dV/dK of batch `nd` as soon as its P/dS tiles are written -- whichever becomes ready first.  Waiting for
-      // them in a fixed order left the tensor core idle for a whole TMA latency per batch: the stage of batch n+2
-      // is only freed by dV/dK of batch n, so a thread blocked on that stage could not issue dV/dK of batch n+1.
+      auto issue_dq = [&](int n) {
+        const uint64_t ads = (n & 1) ? dDSk[1] : dDSk[0];
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)   // contraction over the 64 keys, 16 per step
+          umma_ss(tmem + kColDQ, umma_desc_advance(ads, ks * 32), umma_desc_advance(dKmn, ks * 2048), idesc_dq, ks ? 1u : 0u);
+        umma_commit(dq_full);
+        umma_commit(pds_free + 8 * (n & 1));
+        ++ndq;
+      };
+      // Event loop: dV/dK of batch `nd` is issued as soon as its P/dS tiles are written, S/dP of batch `ns` as soon as
+      // its Q/dO stage has landed and its TMEM buffer is free, the dQ partial of a selected batch as soon as the
+      // soft-max warps have read the previous partial out of its accumulator -- whichever becomes ready first.
+      // Waiting for them in a fixed order left the tensor core idle for a whole TMA latency per batch: the stage of
+      // batch n+2 is only freed by dV/dK of batch n, so a thread blocked on that stage could not issue dV/dK of
+      // batch n+1.
       int ns = 0, nd = 0;
       uint64_t t_idle = 0;
-      while (ok && nd < nb) {
+      while (ok && (nd < nb || dq_pending >= 0)) {
         bool progressed = false;
+        if (dq_pending >= 0 && (ndq == 0 || mbar_test(dq_free, (ndq - 1) & 1))) {
+          tc_fence_after();
+          issue_dq(dq_pending);
+          dq_pending = -1;
+          progressed = true;
+        }
         if (ns < nb && ns < nd + 2 && mbar_test(full0 + 8 * (ns % kStages), (ns / kStages) & 1) &&
             (ns < 2 || mbar_test(sdp_free + 8 * (ns & 1), ((ns >> 1) - 1) & 1))) {
           tc_fence_after();
@@ -291,7 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ++ns;
           progressed = true;
         }
-        if (nd < ns && mbar_test(pds_full + 8 * (nd & 1), (nd >> 1) & 1)) {
+        if (nd < ns && dq_pending < 0 && mbar_test(pds_full + 8 * (nd & 1), (nd >> 1) & 1)) {
           tc_fence_after();
           issue_dkv(nd);
           ++nd;
