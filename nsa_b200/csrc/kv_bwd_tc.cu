@@ -81,7 +81,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   // hold batch n, and P/dS of batch n+1 are written while dV/dK of batch n still read theirs
   const uint32_t full0 = bar_base, empty0 = bar_base + 16, kv_bar = bar_base + 32, sdp_full = bar_base + 40,
                  sdp_free = bar_base + 56, pds_full = bar_base + 72, pds_free = bar_base + 88, acc_full = bar_base + 104,
-                 tmem_slot = bar_base + 112, dq_full = bar_base + 120, dq_free = bar_base + 128;
+                 tmem_slot = bar_base + 112, dq_full = bar_base + 120, dq_free = bar_base + 128, stg_full = bar_base + 136,
+                 stg_free = bar_base + 144;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(full0 + 8 * i, kProd);
@@ -97,6 +98,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(acc_full, 1);
     mbar_init(dq_full, 1);
     mbar_init(dq_free, kSoftThreads);
+    mbar_init(stg_full, kSoftThreads);
+    mbar_init(stg_free, 1);
     fence_mbar_init();
   }
   if (warp == kMmaWarp) tmem_alloc(tmem_slot, kTmemCols);
@@ -359,13 +362,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       return r;
     };
-    // dQ partial of batch m (a selected-branch batch): this thread's half row -> the tile of its list position
+    // dQ partial of batch m (a selected-branch batch): accumulator -> bf16 -> shared memory -> one bulk store.  The
+    // staging area is that batch's own P/dS tile pair (32 KB = 128 rows x 256 bytes): dq_full also says that every MMA
+    // that read the pair has completed, and the soft-max warps write it next only one iteration later, after stg_free.
+    // The 8 tokens' [16 x D] tiles sit at consecutive list positions, i.e. contiguous in dq_part when the KV head has
+    // one 16-head group.  Within a row half the 16-byte chunk c is stored at position c ^ (row & 7) (conflict-free
+    // writes; row & 7 == head & 7, and the reduction kernel undoes it).  Plain stores from the accumulator's layout
+    // (a thread owns a row: 16 bytes per lane at a 256-byte stride) cost a tenth of the kernel in store wavefronts.
     int ndq = 0;
+    bool staged = false;   // a bulk store may still be reading its staging area
+    const bool elected = threadIdx.x == 32 * (kMmaWarp + 1);
     auto drain_dq = [&](int m_batch) {
       ok = ok && mbar_wait(dq_full, ndq & 1, DEV_ERR_FULL_WAIT);
       tc_fence_after();
       const int sub = m_batch / nb_sub, mloc = m_batch % nb_sub;
-      const int i = mloc * kTokB + j;
       uint4 outv[8];
       __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(outv);
       {
@@ -380,13 +390,38 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int e = 0; e < 8; ++e) ho[c * 8 + e] = __floats2bfloat162_rn(vals[c][2 * e], vals[c][2 * e + 1]);
       }
-      if (ok && i < st.nA) {
-        const long long bh = (long long)b * a.Hk + hk;
-        bf16* dst = a.dq_part + (((bh * a.rev_cap + st.ta_lo + i) * G16 + sub) * 16 + head) * D + half * 64;
+      const uint32_t stg = p_s0 + (uint32_t)(m_batch & 1) * 2 * P_TILE;
+      uint8_t* sp = sgen + (stg - sbase) + row * 256 + half * 128;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) reinterpret_cast<uint4*>(dst)[e] = outv[e];
+      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sp + ((c ^ (row & 7)) * 16)) = outv[c];
+      fence_proxy_async();
+      mbar_arrive(stg_full);
+      if (elected) {
+        ok = ok && mbar_wait(stg_full, ndq & 1, DEV_ERR_FULL_WAIT);
+        const int nvalid = min(kTokB, st.nA - mloc * kTokB);
+        if (ok && nvalid > 0) {
+          const long long bh = (long long)b * a.Hk + hk;
+          bf16* dst = a.dq_part + ((bh * a.rev_cap + st.ta_lo + mloc * kTokB) * G16 + sub) * (16 * D);
+          if (G16 == 1) {
+            bulk_store(dst, stg, (uint32_t)nvalid * 16 * D * 2);
+          } else {
+            for (int i = 0; i < nvalid; ++i) bulk_store(dst + (long long)i * G16 * 16 * D, stg + i * 16 * D * 2, 16 * D * 2);
+          }
+        }
+        bulk_commit();
       }
+      staged = true;
       ++ndq;
+    };
+    // before the soft-max warps write a P/dS pair again: the bulk store that used it as staging area has read it
+    auto release_staging = [&]() {
+      if (!staged) return;
+      if (elected) {
+        bulk_wait_read();
+        mbar_arrive(stg_free);
+      }
+      ok = ok && mbar_wait(stg_free, (ndq - 1) & 1, DEV_ERR_EMPTY_WAIT);
+      staged = false;
     };
     int br1, br2;
     bool live1, live2;
@@ -459,6 +494,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = mbar_wait(pds_free + 8 * buf, (use - 1) & 1, DEV_ERR_EMPTY_WAIT);   // dV/dK of batch n-2 have read this pair
         if (!ok) break;
       }
+      release_staging();
+      if (!ok) break;
       // this thread's half of row `row` of the [128 x 64] bf16 tiles: 4 chunks of 16 bytes at swizzled positions
       uint8_t* prow = sgen + (p_s0 - sbase) + buf * 2 * P_TILE + row * 128;
       uint8_t* drow = prow + P_TILE;
@@ -474,6 +511,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (emit_dq && n > 0 && ((n - 1) % nb_sub) < nbA) drain_dq(n - 1);
     }
     if (emit_dq && ok && nb > 0 && ((nb - 1) % nb_sub) < nbA) drain_dq(nb - 1);
+    if (emit_dq && elected) bulk_wait_all();   // the staging area must outlive the last store's read
     // ---- epilogue: dV^T / dK^T [d lanes x 64 key columns] -> global ---------------------------------------
     if (ok && nb > 0) ok = mbar_wait(acc_full, 0, DEV_ERR_FULL_WAIT);
     tc_fence_after();

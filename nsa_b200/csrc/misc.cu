@@ -291,12 +291,17 @@ __global__ void __launch_bounds__(256) sel_dq_reduce_kernel(const RevArgs a, con
     if (s1 >= 0) add(v1);
   }
   const int Hq = a.H * G16 * 16;
-  uint4* dst = reinterpret_cast<uint4*>(dq + ((bt * Hq) + (long long)(h * G16 + sub) * 16) * D) + hb * (8 * D / 8) + lane;
+  // the partial tiles keep the staging layout of the kernel that wrote them: within a 128-byte half row the 16-byte
+  // chunk c sits at position c ^ (head & 7).  All tiles share it, so the sum is formed in place and undone here:
+  // vector u = 32 i + lane of this half tile is row u / 16, position u % 8.
+  uint4* dst = reinterpret_cast<uint4*>(dq + ((bt * Hq) + (long long)(h * G16 + sub) * 16) * D) + hb * (8 * D / 8);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     float prev[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const int u = 32 * i + lane;
+    const int ud = (u & ~7) | ((u & 7) ^ ((u >> 4) & 7));
     if (accumulate) {
-      const uint4 v = dst[32 * i];
+      const uint4 v = dst[ud];
       const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -310,7 +315,7 @@ __global__ void __launch_bounds__(256) sel_dq_reduce_kernel(const RevArgs a, con
 #pragma unroll
     for (int k = 0; k < 4; ++k)
       ho[k] = __floats2bfloat162_rn(fmaf(acc[i][2 * k], scale, prev[2 * k]), fmaf(acc[i][2 * k + 1], scale, prev[2 * k + 1]));
-    dst[32 * i] = o;
+    dst[ud] = o;
   }
 }
 

@@ -153,6 +153,18 @@ def test_selection_and_window_fwd_bwd(nsa, D, BS, S, Hq, Hkv, T, window):
     nsa._lib.device_status()
 
 
+@pytest.mark.parametrize("case", [(128, 64, 4, 32, 2, 384, 100), (128, 64, 20, 16, 1, 450, 0)])
+def test_selection_bwd_query_major_dq(nsa, case):
+    """The same comparison with the small workspace: the selected branch's dQ then comes from the query-major kernel
+    instead of the key-major kernel's per-visit partial tiles (the default, which the test above covers)."""
+    old = nsa._lib.SEL_DQ_FROM_KV
+    nsa._lib.SEL_DQ_FROM_KV = False
+    try:
+        test_selection_and_window_fwd_bwd(nsa, *case)
+    finally:
+        nsa._lib.SEL_DQ_FROM_KV = old
+
+
 def test_selection_varlen_cu_seqlens(nsa):
     """parallel_nsa with cu_seqlens (packed sequences of different lengths, batch 1): block indices and masks are
     relative to each sequence, as in the reference's varlen indexing (nsa/selection_attn.py:419-425).  Forward and
