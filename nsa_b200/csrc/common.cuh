@@ -283,6 +283,15 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm,
 __device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
 }
+// The same with an L2 evict-first policy: data that is written once and read once much later should not displace
+// lines other CTAs are about to re-read.
+__device__ __forceinline__ void bulk_store_evict_first(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile(
+      "{ .reg .b64 pol; createpolicy.fractional.L2::evict_first.b64 pol, 1.0;\n"
+      "cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, pol; }" ::"l"(dst),
+      "r"(src), "r"(bytes)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All of this thread's bulk stores have read their shared-memory source (it may be overwritten).
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

@@ -403,9 +403,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           const long long bh = (long long)b * a.Hk + hk;
           bf16* dst = a.dq_part + ((bh * a.rev_cap + st.ta_lo + mloc * kTokB) * G16 + sub) * (16 * D);
           if (G16 == 1) {
-            bulk_store(dst, stg, (uint32_t)nvalid * 16 * D * 2);
+            bulk_store_evict_first(dst, stg, (uint32_t)nvalid * 16 * D * 2);
           } else {
-            for (int i = 0; i < nvalid; ++i) bulk_store(dst + (long long)i * G16 * 16 * D, stg + i * 16 * D * 2, 16 * D * 2);
+            for (int i = 0; i < nvalid; ++i) bulk_store_evict_first(dst + (long long)i * G16 * 16 * D, stg + i * 16 * D * 2, 16 * D * 2);
           }
         }
         bulk_commit();
