@@ -33,8 +33,10 @@ constexpr int kProd = 3;                   // TMA producer warps (a warp's TMA i
                                            // ~900 cycles each whatever their size, so the boxes of a batch are
                                            // spread over several warps and issued by one instruction per warp)
 constexpr int kMmaWarp = kProd;            // warps 0..kProd-1 TMA, warp kProd MMA, the next eight soft-max / epilogue
-constexpr int kThreads = (kProd + 1 + 8) * 32;
+constexpr int kDrainWarp = kProd + 1 + 8;   // four more warps read the dQ partials out of tensor memory
+constexpr int kThreads = (kProd + 1 + 8 + 4) * 32;   // 512: four warpgroups, registers redistributed by setmaxnreg
 constexpr int kSoftThreads = 256;          // two threads per row: key columns 0-31 and 32-63
+constexpr int kDrainThreads = 128;         // one thread per row
 constexpr int kTokB = 8;                   // tokens per batch (x16 heads = 128 rows)
 constexpr uint32_t KV_PANEL = 64 * 128;    // [64 keys][64 ch]
 constexpr uint32_t KV_TILE = 2 * KV_PANEL; // 16 KB
@@ -82,7 +84,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t full0 = bar_base, empty0 = bar_base + 16, kv_bar = bar_base + 32, sdp_full = bar_base + 40,
                  sdp_free = bar_base + 56, pds_full = bar_base + 72, pds_free = bar_base + 88, acc_full = bar_base + 104,
                  tmem_slot = bar_base + 112, dq_full = bar_base + 120, dq_free = bar_base + 128, stg_full = bar_base + 136,
-                 stg_free = bar_base + 144;
+                 stg_free = bar_base + 144;   // stg_free: two barriers, one per P/dS pair
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(full0 + 8 * i, kProd);
@@ -97,9 +99,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(acc_full, 1);
     mbar_init(dq_full, 1);
-    mbar_init(dq_free, kSoftThreads);
-    mbar_init(stg_full, kSoftThreads);
+    mbar_init(dq_free, kDrainThreads);
+    mbar_init(stg_full, kDrainThreads);
     mbar_init(stg_free, 1);
+    mbar_init(stg_free + 8, 1);
     fence_mbar_init();
   }
   if (warp == kMmaWarp) tmem_alloc(tmem_slot, kTmemCols);
@@ -154,6 +157,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int nb = skip ? 0 : nb_sub * G16;   // batches of this CTA
   const bool emit_dq = MODE == 0 && a.dq_part != nullptr;   // selected-branch batches also leave their dQ partial
 
+  // 512 threads start with 128 registers each; the soft-max warps need 168.  Warps 0-3 (TMA, MMA) and 12-15 (drain)
+  // give registers back, warps 4-11 take them (each instruction is executed by a whole warpgroup).
+  // Each role's code follows its own setmaxnreg, so the compiler allocates registers for it under that budget.
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
   if (!skip && warp < kProd) {
     // ------------------------------- TMA producers -----------------------------------------------
     // A batch of gathered tokens (a reverse-index list) is 32 boxes of 2 KB: (token j, Q or dO, column panel).  Box
@@ -318,7 +326,82 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       umma_commit(acc_full);
     }
-  } else if (!skip && warp > kMmaWarp) {
+  }
+  } else if (warp >= kDrainWarp) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+  if (!skip) {
+    // ------------------------------- drain warps: dQ partials, one row per thread ------------------
+    // dQ partial of a selected batch: accumulator -> bf16 -> shared memory -> one bulk store.  The staging area is that
+    // batch's own P/dS tile pair (32 KB = 128 rows x 256 bytes): dq_full also says that every MMA that read the pair
+    // has completed, and the soft-max warps write it again (batch n+2) only after stg_free.  The 8 tokens' [16 x D]
+    // tiles sit at consecutive list positions, i.e. contiguous in dq_part when the KV head has one 16-head group.
+    // Within a 128-byte half row the 16-byte chunk c is stored at position c ^ (row & 7) (conflict-free writes;
+    // row & 7 == head & 7, and the reduction kernel undoes it).  Plain stores from the accumulator's layout (a thread
+    // owns a row: 16 bytes per lane at a 256-byte stride) cost a tenth of the kernel in store wavefronts, and reading
+    // the partials out in the soft-max warps delayed the next batch's soft-max.
+    if (emit_dq) {
+      const int quad = warp & 3;
+      const int row = 32 * quad + lane;
+      const uint32_t lane_addr = (uint32_t)(32 * quad) << 16;
+      const bool elected = warp == kDrainWarp && lane == 0;
+      bool ok = true;
+      int k = 0;   // partials drained so far
+      for (int n = 0; ok && n < nb; ++n) {
+        const int sub = n / nb_sub, mloc = n % nb_sub;
+        if (mloc >= nbA) continue;
+        ok = mbar_wait(dq_full, k & 1, DEV_ERR_FULL_WAIT);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t stg = p_s0 + (uint32_t)(n & 1) * 2 * P_TILE;
+        uint8_t* sp = sgen + (stg - sbase) + row * 256;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {   // 32 columns at a time
+          float vals[2][16];
+          tmem_ld16(tmem + lane_addr + kColDQ + q4 * 32, vals[0]);
+          tmem_ld16(tmem + lane_addr + kColDQ + q4 * 32 + 16, vals[1]);
+          tmem_ld_wait();
+          if (q4 == 3) {
+            tc_fence_before();
+            mbar_arrive(dq_free);   // the accumulator is in registers: the next partial may be issued
+          }
+#pragma unroll
+          for (int c2 = 0; c2 < 4; ++c2) {   // four 16-byte chunks
+            const float* f = &vals[c2 >> 1][(c2 & 1) * 8];
+            uint4 o;
+            __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ho[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+            const int cc = q4 * 4 + c2;       // chunk 0..15 of the row: half cc >> 3, position (cc & 7) ^ (row & 7)
+            *reinterpret_cast<uint4*>(sp + (cc >> 3) * 128 + (((cc & 7) ^ (row & 7)) * 16)) = o;
+          }
+        }
+        fence_proxy_async();
+        mbar_arrive(stg_full);
+        if (elected) {
+          ok = mbar_wait(stg_full, k & 1, DEV_ERR_FULL_WAIT);
+          const int nvalid = min(kTokB, st.nA - mloc * kTokB);
+          if (ok && nvalid > 0) {
+            const long long bh = (long long)b * a.Hk + hk;
+            bf16* dst = a.dq_part + ((bh * a.rev_cap + st.ta_lo + mloc * kTokB) * G16 + sub) * (16 * D);
+            if (G16 == 1) {
+              bulk_store_evict_first(dst, stg, (uint32_t)nvalid * 16 * D * 2);
+            } else {
+              for (int i = 0; i < nvalid; ++i)
+                bulk_store_evict_first(dst + (long long)i * G16 * 16 * D, stg + i * 16 * D * 2, 16 * D * 2);
+            }
+          }
+          bulk_commit();
+          bulk_wait_read();                       // the pair may be written again
+          mbar_arrive(stg_free + 8 * (n & 1));
+        }
+        ++k;
+      }
+      if (elected) bulk_wait_all();
+    }
+  }
+  } else {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+  if (!skip) {
     // ------------------------------- soft-max warps: one (token, head) row per thread --------------
     const int quad = warp & 3;
     const int half = (warp - kMmaWarp - 1) >> 2; // which 32 key columns this thread owns
@@ -362,67 +445,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       return r;
     };
-    // dQ partial of batch m (a selected-branch batch): accumulator -> bf16 -> shared memory -> one bulk store.  The
-    // staging area is that batch's own P/dS tile pair (32 KB = 128 rows x 256 bytes): dq_full also says that every MMA
-    // that read the pair has completed, and the soft-max warps write it next only one iteration later, after stg_free.
-    // The 8 tokens' [16 x D] tiles sit at consecutive list positions, i.e. contiguous in dq_part when the KV head has
-    // one 16-head group.  Within a row half the 16-byte chunk c is stored at position c ^ (row & 7) (conflict-free
-    // writes; row & 7 == head & 7, and the reduction kernel undoes it).  Plain stores from the accumulator's layout
-    // (a thread owns a row: 16 bytes per lane at a 256-byte stride) cost a tenth of the kernel in store wavefronts.
-    int ndq = 0;
-    bool staged = false;   // a bulk store may still be reading its staging area
-    const bool elected = threadIdx.x == 32 * (kMmaWarp + 1);
-    auto drain_dq = [&](int m_batch) {
-      ok = ok && mbar_wait(dq_full, ndq & 1, DEV_ERR_FULL_WAIT);
-      tc_fence_after();
-      const int sub = m_batch / nb_sub, mloc = m_batch % nb_sub;
-      uint4 outv[8];
-      __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(outv);
-      {
-        float vals[4][16];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld16(tmem + lane_addr + kColDQ + half * 64 + c * 16, vals[c]);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(dq_free);   // the accumulator is in registers: the next partial may be issued
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) ho[c * 8 + e] = __floats2bfloat162_rn(vals[c][2 * e], vals[c][2 * e + 1]);
-      }
-      const uint32_t stg = p_s0 + (uint32_t)(m_batch & 1) * 2 * P_TILE;
-      uint8_t* sp = sgen + (stg - sbase) + row * 256 + half * 128;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sp + ((c ^ (row & 7)) * 16)) = outv[c];
-      fence_proxy_async();
-      mbar_arrive(stg_full);
-      if (elected) {
-        ok = ok && mbar_wait(stg_full, ndq & 1, DEV_ERR_FULL_WAIT);
-        const int nvalid = min(kTokB, st.nA - mloc * kTokB);
-        if (ok && nvalid > 0) {
-          const long long bh = (long long)b * a.Hk + hk;
-          bf16* dst = a.dq_part + ((bh * a.rev_cap + st.ta_lo + mloc * kTokB) * G16 + sub) * (16 * D);
-          if (G16 == 1) {
-            bulk_store_evict_first(dst, stg, (uint32_t)nvalid * 16 * D * 2);
-          } else {
-            for (int i = 0; i < nvalid; ++i) bulk_store_evict_first(dst + (long long)i * G16 * 16 * D, stg + i * 16 * D * 2, 16 * D * 2);
-          }
-        }
-        bulk_commit();
-      }
-      staged = true;
-      ++ndq;
-    };
-    // before the soft-max warps write a P/dS pair again: the bulk store that used it as staging area has read it
-    auto release_staging = [&]() {
-      if (!staged) return;
-      if (elected) {
-        bulk_wait_read();
-        mbar_arrive(stg_free);
-      }
-      ok = ok && mbar_wait(stg_free, (ndq - 1) & 1, DEV_ERR_EMPTY_WAIT);
-      staged = false;
-    };
+    // With dQ partials: the drain warps stage the partial of a selected batch n in that batch's own P/dS pair; the pair
+    // is written again for batch n+2 only after their bulk store has read it (stg_free of that pair).
+    int nstg[2] = {0, 0};   // waits done on each pair's stg_free
     int br1, br2;
     bool live1, live2;
     int t1 = row_token(0, br1, live1);
@@ -494,8 +519,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = mbar_wait(pds_free + 8 * buf, (use - 1) & 1, DEV_ERR_EMPTY_WAIT);   // dV/dK of batch n-2 have read this pair
         if (!ok) break;
       }
-      release_staging();
-      if (!ok) break;
+      if (emit_dq && n >= 2 && ((n - 2) % nb_sub) < nbA) {
+        ok = mbar_wait(stg_free + 8 * buf, nstg[buf] & 1, DEV_ERR_EMPTY_WAIT);
+        ++nstg[buf];
+        if (!ok) break;
+      }
       // this thread's half of row `row` of the [128 x 64] bf16 tiles: 4 chunks of 16 bytes at swizzled positions
       uint8_t* prow = sgen + (p_s0 - sbase) + buf * 2 * P_TILE + row * 128;
       uint8_t* drow = prow + P_TILE;
@@ -507,11 +535,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       fence_proxy_async();
       mbar_arrive(pds_full + 8 * buf);
-      // the previous batch's dQ partial is complete by now (its MMAs were issued a whole batch ago)
-      if (emit_dq && n > 0 && ((n - 1) % nb_sub) < nbA) drain_dq(n - 1);
     }
-    if (emit_dq && ok && nb > 0 && ((nb - 1) % nb_sub) < nbA) drain_dq(nb - 1);
-    if (emit_dq && elected) bulk_wait_all();   // the staging area must outlive the last store's read
     // ---- epilogue: dV^T / dK^T [d lanes x 64 key columns] -> global ---------------------------------------
     if (ok && nb > 0) ok = mbar_wait(acc_full, 0, DEV_ERR_FULL_WAIT);
     tc_fence_after();
@@ -543,6 +567,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
+  }
   }
   tc_fence_before();
   __syncthreads();
