@@ -198,8 +198,9 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
     idx = torch.empty(B, T, Hkv, c["n_sel"], dtype=torch.int32, device=q4.device)
     dq, dk, dv = torch.empty_like(q4), torch.empty_like(k4), torch.empty_like(v4)
     dck, dcv = torch.empty_like(ck), torch.empty_like(cv)
-    ws1 = torch.empty(_lib.sel_swa_bwd_workspace_bytes(B, T, T, Hq, Hkv, D, c["n_sel"], c["sel_block"]), dtype=torch.uint8,
-                      device=q4.device)
+    ws1 = torch.empty(max(_lib.sel_swa_bwd_workspace_bytes(B, T, T, Hq, Hkv, D, c["n_sel"], c["sel_block"]),
+                          L.nsa_sel_swa_fwd_workspace_bytes(B, T, T, Hq, Hkv, D, c["n_sel"], c["sel_block"])),
+                      dtype=torch.uint8, device=q4.device)
     ws2 = torch.empty(L.nsa_cmp_attn_bwd_workspace_bytes(B, T, Tc, Hkv, D), dtype=torch.uint8, device=q4.device)
     P, S = _lib.ptr, _lib.stream
     wk = mod.compressor.compressor_k.weight.detach().permute(2, 1, 0).reshape(c["block"] * D, D).contiguous()
@@ -224,6 +225,11 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
         "sel_fwd": lambda: L.nsa_sel_swa_fwd(P(q4), P(k4), P(v4), P(idx), 0, None, P(o_slc), P(lse_slc), None, None, None,
                                              None, None, None, None, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"], 0,
                                              scale, S()),
+        # option, not in a module step: the same forward key-major on the tensor cores (reverse index, one CTA per key
+        # block over the queries that selected it, per-visit partial tiles, slot-order merge)
+        "sel_fwd_keymajor(option)": lambda: L.nsa_sel_swa_fwd_ws(
+            P(q4), P(k4), P(v4), P(idx), 0, None, P(o_slc), P(lse_slc), None, None, None, None, None, None, None, P(ws1),
+            ws1.numel(), B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"], 0, scale, T, 0, S()),
         "gather_probe": lambda: L.nsa_gather_probe(P(k4), P(v4), P(idx), 0, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"],
                                                    S()),
         "swa_fwd": lambda: L.nsa_sel_swa_fwd(P(q4), P(k4), P(v4), None, 0, None, None, None, P(o_swa), P(lse_swa), None,

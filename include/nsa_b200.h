@@ -159,6 +159,18 @@ int nsa_sel_swa_fwd_sharded(const void* q, const void* k, const void* v, const v
                             const void* g_slc, const void* g_swa, const void* o_cmp, const void* g_cmp, void* o, int B,
                             int T, int Hq, int Hkv, int D, int S, int BS, int window, float scale, int Tq, int q0,
                             void* stream);
+/* nsa_sel_swa_fwd_sharded with a workspace (nsa_sel_swa_fwd_workspace_bytes; Tq = T, q0 = 0 when not sharded).  With it,
+ * head_dim 128, 64-key blocks, at most 32 selections and a multiple of 16 query heads per KV head, the selected branch
+ * runs key-major on the tensor cores: a reverse index of the selection is built, one CTA per key block takes the queries
+ * that selected it in batches of 8 tokens x 16 heads (tcgen05 S = Q K^T and P V), every visit leaves a [16 x D] bf16 tile
+ * and (max, sum) per row, and a second kernel merges a token's visits in slot order (no atomics).  A block's K and V are
+ * then read once per CTA instead of once per visiting query.  Results equal the query-major kernel's up to the bf16
+ * rounding of the per-visit tiles.  Without the workspace (ws NULL or too small) this is nsa_sel_swa_fwd_sharded. */
+int nsa_sel_swa_fwd_ws(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                       void* o_slc, float* lse_slc, void* o_swa, float* lse_swa, const void* g_slc, const void* g_swa,
+                       const void* o_cmp, const void* g_cmp, void* o, void* ws, size_t ws_bytes, int B, int T, int Hq,
+                       int Hkv, int D, int S, int BS, int window, float scale, int Tq, int q0, void* stream);
+size_t nsa_sel_swa_fwd_workspace_bytes(int B, int T, int Tq, int Hq, int Hkv, int D, int S, int BS);
 int nsa_sel_swa_bwd_sharded(const void* q, const void* k, const void* v, const void* idx, int idx64,
                             const int32_t* counts, const void* dout_slc, const float* lse_slc, const float* delta_slc,
                             const void* gate_slc, const void* dout_swa, const float* lse_swa, const float* delta_swa,

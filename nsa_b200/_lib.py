@@ -37,6 +37,8 @@ SIGNATURES = {
     "nsa_cmp_attn_fwd_sharded": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, I, I, P]),
     "nsa_cmp_attn_bwd_sharded": (I, [P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I, I, F, I, I, P]),
     "nsa_sel_swa_fwd_sharded": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P]),
+    "nsa_sel_swa_fwd_ws": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, Z, I, I, I, I, I, I, I, I, F, I, I, P]),
+    "nsa_sel_swa_fwd_workspace_bytes": (Z, [I, I, I, I, I, I, I, I]),
     "nsa_sel_swa_bwd_sharded": (I, [P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, P, P, P, Z, I, I, I, I, I, I, I, I,
                                     F, I, I, P]),
     "nsa_sel_swa_bwd_fused": (I, [P, P, P, P, I, P] + [P] * 11 + [P, I, P, P, P, Z, I, I, I, I, I, I, I, I, F, I, I, P]),
@@ -94,6 +96,16 @@ def sel_swa_bwd_workspace_bytes(B, T, Tq, Hq, Hkv, D, S, BS):
     if SEL_DQ_FROM_KV and D == 128 and BS == 64:
         return lib().nsa_sel_swa_bwd_workspace_bytes_dq(B, T, Tq, Hq, Hkv, D, S, BS)
     return lib().nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, S, BS)
+
+
+# Selected-branch forward key-major on the tensor cores (needs a workspace of about B*Tq*Hq*S*D*2 bytes) or query-major.
+SEL_FWD_KV = False
+
+
+def sel_swa_fwd_workspace_bytes(B, T, Tq, Hq, Hkv, D, S, BS):
+    if SEL_FWD_KV and D == 128 and BS == 64 and S <= 32 and Hq % (16 * Hkv) == 0:
+        return lib().nsa_sel_swa_fwd_workspace_bytes(B, T, Tq, Hq, Hkv, D, S, BS)
+    return 0
 
 
 def ptr(t):

@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(HERE, "lib", "obj")
 LIB = os.path.join(LIBDIR, "libnsa_b200.so")
-SOURCES = ["api.cu", "tmap.cu", "sel_attn.cu", "sel_block.cu", "dense_attn.cu", "dense_fwd2_tc.cu", "dense_dq_tc.cu", "kv_bwd.cu", "kv_bwd_tc.cu", "compress.cu", "compress_tc.cu", "misc.cu", "gate.cu", "gather_probe.cu", "decode.cu"]
+SOURCES = ["api.cu", "tmap.cu", "sel_attn.cu", "sel_block.cu", "sel_fwd_kv_tc.cu", "dense_attn.cu", "dense_fwd2_tc.cu", "dense_dq_tc.cu", "kv_bwd.cu", "kv_bwd_tc.cu", "compress.cu", "compress_tc.cu", "misc.cu", "gate.cu", "gather_probe.cu", "decode.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

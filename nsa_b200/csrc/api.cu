@@ -64,7 +64,7 @@ int nsa_device_status(void) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(1000 + (int)e, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
   int worst = 0, v = 0;
-  int (*fns[])(int*) = {sel_status, sel_block_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_dq_tc_status, gather_probe_status, dense_tc2_status, decode_status};
+  int (*fns[])(int*) = {sel_status, sel_block_status, dense_status, kv_status, compress_status, misc_status, compress_tc_status, kv_tc_status, dense_dq_tc_status, gather_probe_status, dense_tc2_status, decode_status, sel_fwd_kv_status};
   for (auto f : fns) {
     v = 0;
     const int rc = f(&v);
@@ -306,10 +306,20 @@ static int check_bs(const char* who, int BS) {
   return 0;
 }
 
+// Workspace of the key-major selected forward: the reverse index (as in the backward), its inverse [B,Tq,Hkv,S] int32,
+// one [16 x D] bf16 tile and 16 (max, sum) pairs per (list position, 16-head sub-group).
+size_t nsa_sel_swa_fwd_workspace_bytes(int B, int T, int Tq, int Hq, int Hkv, int D, int S, int BS) {
+  if (BS <= 0 || Hkv <= 0) return 0;
+  const size_t ent = (size_t)B * Tq * Hkv * S;
+  const size_t g = (size_t)(Hq / Hkv);
+  return nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, S, BS) + align_up(ent * 4, 256) + align_up(ent * g * D * 2, 256) +
+         align_up(ent * g * 8, 256);
+}
+
 static int sel_swa_fwd_impl(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
                     void* o_slc, float* lse_slc, void* o_swa, float* lse_swa, const void* g_slc, const void* g_swa,
                     const void* o_cmp, const void* g_cmp, void* o, int B, int T, int Hq, int Hkv, int D, int S, int BS,
-                    int window, float scale, int Tq, int q0, void* stream) {
+                    int window, float scale, int Tq, int q0, void* stream, void* ws = nullptr, size_t ws_bytes = 0) {
   const bool sharded = (Tq != T) || (q0 != 0);
   if (Tq <= 0 || q0 < 0 || q0 + Tq > T) return fail(-12, "%s: query shard [%d, %d) is outside the sequence of %d tokens", "nsa_sel_swa_fwd", q0, q0 + Tq, T);
   (void)sharded;
@@ -322,11 +332,40 @@ static int sel_swa_fwd_impl(const void* q, const void* k, const void* v, const v
     rc = check_bs("nsa_sel_swa_fwd", BS);
     if (rc) return rc;
     if (S <= 0) return fail(-1, "nsa_sel_swa_fwd: no selected blocks");
-    SelArgs a = {};
-    a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64; a.counts = counts;
-    a.o = (bf16*)o_slc; a.lse = lse_slc; a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS; a.scale = scale;
-    rc = launch_sel_fwd(a, D, s);
-    if (rc) return rc;
+    SelKvArgs ka = {};
+    ka.q = (const bf16*)q; ka.k = (const bf16*)k; ka.v = (const bf16*)v; ka.o = (bf16*)o_slc; ka.lse = lse_slc;
+    ka.B = B; ka.T = T; ka.Tq = Tq; ka.q0 = q0; ka.Hq = Hq; ka.Hk = Hkv; ka.S = S; ka.BS = BS; ka.scale = scale;
+    if (ws && sel_fwd_kv_supported(ka, D) && ws_bytes >= nsa_sel_swa_fwd_workspace_bytes(B, T, Tq, Hq, Hkv, D, S, BS)) {
+      // key-major: reverse index, then one CTA per key block over the queries that selected it, then the per-token merge
+      const int NB = (T + BS - 1) / BS;
+      const size_t bh = (size_t)B * Hkv, ent = (size_t)B * Tq * Hkv * S, g = (size_t)(Hq / Hkv);
+      char* p = (char*)ws;
+      RevArgs r = {};
+      r.idx = idx; r.idx64 = idx64; r.counts = counts; r.B = B; r.T = T; r.Tq = Tq; r.q0 = q0; r.H = Hkv; r.S = S; r.BS = BS; r.NB = NB;
+      r.hist = (int*)p;
+      p += align_up(bh * NB * NB * 4, 256);
+      r.rev_ptr = (int*)p;
+      p += align_up(bh * (NB + 1) * 4, 256);
+      r.rev_tok = (int*)p;
+      p += align_up(bh * (size_t)T * S * 4, 256);
+      r.cap = (long long)Tq * S;
+      r.inv = (int*)p;
+      p += align_up(ent * 4, 256);
+      ka.part = (bf16*)p;
+      p += align_up(ent * g * D * 2, 256);
+      ka.stats = (float*)p;
+      rc = launch_build_rev(r, s);
+      if (rc) return rc;
+      ka.rev_ptr = r.rev_ptr; ka.rev_tok = r.rev_tok; ka.rev_cap = r.cap;
+      rc = launch_sel_fwd_kv(ka, r, s);
+      if (rc) return rc;
+    } else {
+      SelArgs a = {};
+      a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.idx = idx; a.idx64 = idx64; a.counts = counts;
+      a.o = (bf16*)o_slc; a.lse = lse_slc; a.B = B; a.T = T; a.Tq = Tq; a.q0 = q0; a.Hq = Hq; a.Hkv = Hkv; a.S = S; a.BS = BS; a.scale = scale;
+      rc = launch_sel_fwd(a, D, s);
+      if (rc) return rc;
+    }
   }
   if (window > 0) {
     if (!o_swa || !lse_swa) return fail(-1, "nsa_sel_swa_fwd: o_swa / lse_swa is null");
@@ -357,6 +396,13 @@ int nsa_sel_swa_fwd_sharded(const void* q, const void* k, const void* v, const v
                     const void* o_cmp, const void* g_cmp, void* o, int B, int T, int Hq, int Hkv, int D, int S, int BS,
                     int window, float scale, int Tq, int q0, void* stream) {
   return sel_swa_fwd_impl(q, k, v, idx, idx64, counts, o_slc, lse_slc, o_swa, lse_swa, g_slc, g_swa, o_cmp, g_cmp, o, B, T, Hq, Hkv, D, S, BS, window, scale, Tq, q0, stream);
+}
+
+int nsa_sel_swa_fwd_ws(const void* q, const void* k, const void* v, const void* idx, int idx64, const int32_t* counts,
+                    void* o_slc, float* lse_slc, void* o_swa, float* lse_swa, const void* g_slc, const void* g_swa,
+                    const void* o_cmp, const void* g_cmp, void* o, void* ws, size_t ws_bytes, int B, int T, int Hq, int Hkv,
+                    int D, int S, int BS, int window, float scale, int Tq, int q0, void* stream) {
+  return sel_swa_fwd_impl(q, k, v, idx, idx64, counts, o_slc, lse_slc, o_swa, lse_swa, g_slc, g_swa, o_cmp, g_cmp, o, B, T, Hq, Hkv, D, S, BS, window, scale, Tq, q0, stream, ws, ws_bytes);
 }
 
 int nsa_cmp_attn_bwd_fused(const void* q, const void* ck, const void* cv, const void* o_cmp, const float* lse, const void* dout,

@@ -295,6 +295,8 @@ __device__ __forceinline__ void bulk_store_evict_first(void* dst, uint32_t src, 
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All of this thread's bulk stores have read their shared-memory source (it may be overwritten).
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All but the most recent of this thread's bulk-store groups have read their source.
+__device__ __forceinline__ void bulk_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // All of this thread's bulk stores are complete.
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Plain bulk copy global -> shared; src/dst 16-byte aligned, bytes a multiple of 16.

@@ -208,6 +208,40 @@ struct RevArgs {
   int* inv;       // optional [B,Tq,H,S]: for every valid (row, slot) its position in the (b,h) list of rev_tok
 };
 int launch_build_rev(const RevArgs& a, cudaStream_t s);
+#ifdef __CUDACC__
+// The block that slot s of a row selects, or -1 if the slot does not count (beyond the row's count, out of range, or a
+// block that starts after the token).  `row` is the local (batch, token, head) row of idx/counts, `t` the token's
+// sequence position.  Every kernel that walks the selection uses this one rule.
+__device__ __forceinline__ int rev_block(const RevArgs& a, long long row, int s, int t) {
+  int cnt = a.S;
+  if (a.counts) cnt = min(cnt, a.counts[row]);
+  if (s >= cnt) return -1;
+  long long v = a.idx64 ? reinterpret_cast<const long long*>(a.idx)[row * a.S + s]
+                        : (long long)reinterpret_cast<const int*>(a.idx)[row * a.S + s];
+  if (v < 0 || v >= a.NB || v * a.BS > t) return -1;
+  return (int)v;
+}
+#endif
+// Selected attention forward, key-major (sel_fwd_kv_tc.cu): one CTA per 64-key block, the queries that selected it in
+// batches of 8 tokens x 16 heads from the reverse index; per visit a [16 x D] bf16 tile of unnormalised output and
+// (max, sum) per row, merged per token in slot order by a second kernel.
+struct SelKvArgs {
+  const bf16* q;        // [B,Tq,Hq,D]
+  const bf16* k;        // [B,T,Hk,D]
+  const bf16* v;
+  bf16* o;              // [B,Tq,Hq,D]
+  float* lse;           // [B,Tq,Hq] natural log
+  const int* rev_ptr;   // reverse index (launch_build_rev, with inv)
+  const int* rev_tok;
+  long long rev_cap;
+  bf16* part;           // [B,Hk,rev_cap,G16][16][D]
+  float* stats;         // [B,Hk,rev_cap,G16][16][2]: row maximum (log2 domain, scaled) and sum of probabilities
+  int B, T, Tq, q0, Hq, Hk, S, BS;
+  float scale;
+};
+bool sel_fwd_kv_supported(const SelKvArgs& a, int D);
+int launch_sel_fwd_kv(const SelKvArgs& a, const RevArgs& r, cudaStream_t s);
+int sel_fwd_kv_status(int* out);
 // dq[(b,t), 16-head group] (+)= scale * sum over the valid slots s of part[(b,h) list position inv[row,s]] (fixed slot
 // order).  part holds one [16 heads x D] bf16 tile per (list position, 16-head sub-group), written by the kv-major
 // backward; dq rows of a (token, group) are the same contiguous tile.

@@ -84,17 +84,6 @@ __global__ void combine_kernel(const bf16* __restrict__ a0, const bf16* __restri
 // Replaces the dense boolean block mask of parallel_nsa_kernel_mask (nsa/selection_attn.py:256-273).
 // A stable counting sort by block id in three launches; the order inside every list is ascending in t and
 // independent of scheduling, so the backward is bit-reproducible.
-// `row` is the local (batch, token, head) row of idx/counts; `t` the token's sequence position
-__device__ __forceinline__ int rev_block(const RevArgs& a, long long row, int s, int t) {
-  int cnt = a.S;
-  if (a.counts) cnt = min(cnt, a.counts[row]);
-  if (s >= cnt) return -1;
-  long long v = a.idx64 ? reinterpret_cast<const long long*>(a.idx)[row * a.S + s]
-                        : (long long)reinterpret_cast<const int*>(a.idx)[row * a.S + s];
-  if (v < 0 || v >= a.NB || v * a.BS > t) return -1;
-  return (int)v;
-}
-
 // grid (NB chunks, B*H): histogram of the block ids selected by the BS tokens of one chunk
 __global__ void rev_hist_kernel(const RevArgs a) {
   extern __shared__ int sh[];

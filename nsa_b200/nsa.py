@@ -51,9 +51,11 @@ class _NSACore(torch.autograd.Function):
             _lib.check(L.nsa_cmp_attn_fwd_gated(P(q), P(ck), P(cv), P(o_cmp), P(lse_cmp), P(idx), None, None, None, None,
                                                 None, None, B, T, Tc, Hq, Hkv, D, block, stride, 1 if causal else 0, scale,
                                                 n_sel, pool_k, pool_s, pool_p, score_mode, Tq, q0, S()), "nsa_cmp_attn_fwd")
-        _lib.check(L.nsa_sel_swa_fwd_sharded(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(lse_slc), P(o_swa),
-                                             P(lse_swa), P(g_slc), P(g_swa), P(o_cmp), P(g_cmp), P(o), B, T, Hq, Hkv, D,
-                                             n_sel, sel_block, window, scale, Tq, q0, S()), "nsa_sel_swa_fwd")
+        fws_bytes = _lib.sel_swa_fwd_workspace_bytes(B, T, Tq, Hq, Hkv, D, n_sel, sel_block)
+        fws = torch.empty(fws_bytes, dtype=torch.uint8, device=dev) if fws_bytes else None
+        _lib.check(L.nsa_sel_swa_fwd_ws(P(q), P(k), P(v), P(idx), 0, None, P(o_slc), P(lse_slc), P(o_swa),
+                                        P(lse_swa), P(g_slc), P(g_swa), P(o_cmp), P(g_cmp), P(o), P(fws), fws_bytes, B, T,
+                                        Hq, Hkv, D, n_sel, sel_block, window, scale, Tq, q0, S()), "nsa_sel_swa_fwd")
         ctx.save_for_backward(q, k, v, ck, cv, g_slc, g_swa, g_cmp, o_slc, o_swa, o_cmp, lse_slc, lse_swa, lse_cmp, idx,
                               w_gate)
         ctx.cfg = cfg

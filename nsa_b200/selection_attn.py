@@ -48,11 +48,13 @@ class ParallelNSAFunction(torch.autograd.Function):
         P, i64 = _lib.ptr, 1 if idx.dtype == torch.int64 else 0
         for a, b in (seqs or [(0, T)]):
             sl = slice(a, b)
-            _lib.check(_lib.lib().nsa_sel_swa_fwd(
+            fws_bytes = _lib.sel_swa_fwd_workspace_bytes(B, b - a, b - a, Hq, Hkv, D, S, block_size)
+            fws = torch.empty(fws_bytes, dtype=torch.uint8, device=q.device) if fws_bytes else None
+            _lib.check(_lib.lib().nsa_sel_swa_fwd_ws(
                 P(q[:, sl]), P(k[:, sl]), P(v[:, sl]), P(idx[:, sl]), i64, P(counts[:, sl]) if counts is not None else None,
                 P(o_slc[:, sl]), P(lse_slc[:, sl]), P(o_swa[:, sl]) if o_swa is not None else None,
-                P(lse_swa[:, sl]) if lse_swa is not None else None, None, None, None, None, None,
-                B, b - a, Hq, Hkv, D, S, block_size, window_size, float(scale), _lib.stream()), "nsa_sel_swa_fwd")
+                P(lse_swa[:, sl]) if lse_swa is not None else None, None, None, None, None, None, P(fws), fws_bytes,
+                B, b - a, Hq, Hkv, D, S, block_size, window_size, float(scale), b - a, 0, _lib.stream()), "nsa_sel_swa_fwd")
         ctx.save_for_backward(q, k, v, o_slc, lse_slc, o_swa, lse_swa, idx, counts)
         ctx.meta = (block_size, window_size, float(scale), seqs)
         return o_slc, o_swa

@@ -165,6 +165,19 @@ def test_selection_bwd_query_major_dq(nsa, case):
         nsa._lib.SEL_DQ_FROM_KV = old
 
 
+@pytest.mark.parametrize("case", [(128, 64, 4, 32, 2, 384, 100), (128, 64, 20, 16, 1, 450, 0), (128, 64, 4, 32, 1, 300, 64)])
+def test_selection_fwd_key_major(nsa, case):
+    """The same comparison with the selected branch's forward run key-major on the tensor cores (reverse index, per-visit
+    partial tiles, slot-order merge): an option of nsa_sel_swa_fwd_ws, off by default because it is not faster.  The
+    last case has two 16-head groups per KV head."""
+    old = nsa._lib.SEL_FWD_KV
+    nsa._lib.SEL_FWD_KV = True
+    try:
+        test_selection_and_window_fwd_bwd(nsa, *case)
+    finally:
+        nsa._lib.SEL_FWD_KV = old
+
+
 def test_selection_varlen_cu_seqlens(nsa):
     """parallel_nsa with cu_seqlens (packed sequences of different lengths, batch 1): block indices and masks are
     relative to each sequence, as in the reference's varlen indexing (nsa/selection_attn.py:419-425).  Forward and
