@@ -8,7 +8,10 @@
 // eight soft-max warps (half a row of 64 key columns per thread; lse, delta, gate and the mask are thread-local)
 // form  dS = P (g dP - delta)  with  P = exp(scale S - lse)  and store it as a bf16 tile, and the thread issues
 //     dQ += dS . K                          (A = dS from shared memory, B = K as an MN-major operand)
-// S/dP of tile i+1 are issued as soon as the soft-max warps hold tile i in registers, before dQ of tile i.
+// S/dP of tile i+1 are issued as soon as the soft-max warps hold tile i in registers, before dQ of tile i: a soft-max
+// thread fetches all 64 + 64 values of its half row first and hands the accumulators back at once, so those MMAs run
+// under the whole soft-max of tile i.  That needs about 220 registers in the soft-max warps: the CTA has three
+// warpgroups (warps 0-3: TMA, MMA and two idle warps; warps 4-11 soft-max) and redistributes registers with setmaxnreg.
 #include "kernels.h"
 #include "tc.cuh"
 #include "tmap.h"
@@ -19,7 +22,7 @@ namespace {
 
 constexpr int D = 128;
 constexpr int kTok = 8;
-constexpr int kThreads = 320;                 // warp 0 TMA, warp 1 MMA, warps 2-9 soft-max
+constexpr int kThreads = 384;                 // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-11 soft-max
 constexpr int kSoft = 256;
 constexpr uint32_t PANEL = 128 * 128;         // [128 rows][64 columns] bf16
 constexpr uint32_t TILE = 2 * PANEL;          // 32 KB
@@ -92,6 +95,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int ntile = (a.Tq + kTok - 1) / kTok;
   const long long total = (long long)a.B * HG * ntile;
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 0) {
     // ------------------------------- TMA producer ------------------------------------------------
     uint32_t c = 0, ic = 0;
@@ -222,10 +227,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         umma_commit(dq_full);
       }
     }
+  }
   } else {
     // ------------------------------- soft-max warps ------------------------------------------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 4) >> 2;
     const int row = 32 * quad + lane;
     const int tl = row >> 4, head = row & 15;
     const uint32_t lane_addr = (uint32_t)(32 * quad) << 16;
@@ -325,33 +332,27 @@ __global__ void __launch_bounds__(kThreads, 1)
         const bool full = lo <= 0 && hi >= 64;
         uint32_t dw[32];
         const float nl = -lse2;
+        float s[64], dp[64];
 #pragma unroll
-        for (int q2 = 0; q2 < 2; ++q2) {   // two chunks of 32 columns keep the register footprint down
-          float s[32], dp[32];
+        for (int q4 = 0; q4 < 4; ++q4) {
+          tmem_ld16(tmem + lane_addr + half * 64 + q4 * 16, *reinterpret_cast<float(*)[16]>(&s[q4 * 16]));
+          tmem_ld16(tmem + lane_addr + 128 + half * 64 + q4 * 16, *reinterpret_cast<float(*)[16]>(&dp[q4 * 16]));
+        }
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(sdp_free);   // S and dP of this tile are in registers: the next tile's products may overwrite them
+        if (full) {
 #pragma unroll
-          for (int q4 = 0; q4 < 2; ++q4) {
-            tmem_ld16(tmem + lane_addr + half * 64 + q2 * 32 + q4 * 16, *reinterpret_cast<float(*)[16]>(&s[q4 * 16]));
-            tmem_ld16(tmem + lane_addr + 128 + half * 64 + q2 * 32 + q4 * 16, *reinterpret_cast<float(*)[16]>(&dp[q4 * 16]));
+          for (int e = 0; e < 64; e += 2) {
+            const float p0 = ex2(fmaf(s[e], sl2, nl)), p1 = ex2(fmaf(s[e + 1], sl2, nl));
+            dw[e >> 1] = pack_bf16(p0 * fmaf(gv, dp[e], -del), p1 * fmaf(gv, dp[e + 1], -del));
           }
-          tmem_ld_wait();
-          if (q2 == 1) {
-            tc_fence_before();
-            mbar_arrive(sdp_free);   // S and dP of this tile are in registers
-          }
-          if (full) {
+        } else {
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              const float p0 = ex2(fmaf(s[e], sl2, nl)), p1 = ex2(fmaf(s[e + 1], sl2, nl));
-              dw[q2 * 16 + (e >> 1)] = pack_bf16(p0 * fmaf(gv, dp[e], -del), p1 * fmaf(gv, dp[e + 1], -del));
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              const int e0 = q2 * 32 + e;
-              const float p0 = (e0 >= lo && e0 < hi) ? ex2(fmaf(s[e], sl2, nl)) : 0.f;
-              const float p1 = (e0 + 1 >= lo && e0 + 1 < hi) ? ex2(fmaf(s[e + 1], sl2, nl)) : 0.f;
-              dw[q2 * 16 + (e >> 1)] = pack_bf16(p0 * fmaf(gv, dp[e], -del), p1 * fmaf(gv, dp[e + 1], -del));
-            }
+          for (int e = 0; e < 64; e += 2) {
+            const float p0 = (e >= lo && e < hi) ? ex2(fmaf(s[e], sl2, nl)) : 0.f;
+            const float p1 = (e + 1 >= lo && e + 1 < hi) ? ex2(fmaf(s[e + 1], sl2, nl)) : 0.f;
+            dw[e >> 1] = pack_bf16(p0 * fmaf(gv, dp[e], -del), p1 * fmaf(gv, dp[e + 1], -del));
           }
         }
         if (c > 0) ok = mbar_wait_abortable(ds_free, (c - 1) & 1, 209, abort_flag) && ok;   // dQ of the previous tile read dS
