@@ -29,12 +29,16 @@ namespace nsa {
 namespace {
 
 constexpr int D = 128;
-constexpr int kProd = 3;                   // TMA producer warps (a warp's TMA instructions run one after another,
+constexpr int kProd = 2;                   // TMA producer warps (a warp's TMA instructions run one after another,
                                            // ~900 cycles each whatever their size, so the boxes of a batch are
-                                           // spread over several warps and issued by one instruction per warp)
-constexpr int kMmaWarp = kProd;            // warps 0..kProd-1 TMA, warp kProd MMA, the next eight soft-max / epilogue
-constexpr int kDrainWarp = kProd + 1 + 8;   // four more warps read the dQ partials out of tensor memory
-constexpr int kThreads = (kProd + 1 + 8 + 4) * 32;   // 512: four warpgroups, registers redistributed by setmaxnreg
+                                           // spread over two warps and issued by one instruction per warp)
+constexpr int kMmaWarp = 2;                // issues S and dP
+constexpr int kMma2Warp = 3;               // issues dV, dK and the dQ partials: tcgen05.mma costs its issuing thread
+                                           // ~60 cycles per instruction, so two threads issue the kernel's 32-36 MMAs
+                                           // per batch
+constexpr int kSoftWarp = 4;               // eight soft-max / epilogue warps
+constexpr int kDrainWarp = 12;             // four more warps read the dQ partials out of tensor memory
+constexpr int kThreads = 16 * 32;          // 512: four warpgroups, registers redistributed by setmaxnreg
 constexpr int kSoftThreads = 256;          // two threads per row: key columns 0-31 and 32-63
 constexpr int kDrainThreads = 128;         // one thread per row
 constexpr int kTokB = 8;                   // tokens per batch (x16 heads = 128 rows)
@@ -221,31 +225,27 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (!skip && warp == kMmaWarp) {
-    // ------------------------------- MMA issuer ----------------------------------------------------
+    // ------------------------------- MMA issuer A: S and dP ----------------------------------------
+    // S/dP of batch n is issued as soon as its Q/dO stage has landed and its TMEM buffer is free (the soft-max warps
+    // hold batch n-2 in registers), i.e. ahead of dV/dK of batch n-1, which the second issuer handles.
     if (lane == 0 && nb > 0) {
       constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 64, 0, 0);   // both operands K-major
-      constexpr uint32_t idesc_mn = umma_idesc_bf16(128, 64, 1, 1);   // both operands MN-major
       bool ok = mbar_wait(kv_bar, 0, DEV_ERR_FULL_WAIT);
-      // descriptors of every operand tile are built once; an MMA then costs one 64-bit add per operand
       const uint64_t dK = umma_smem_desc(k_s, 0, 1024), dV = umma_smem_desc(v_s, 0, 1024);
-      uint64_t dQk[kStages], dDOk[kStages], dQmn[kStages], dDOmn[kStages], dP[2], dDS[2];
+      uint64_t dQk[kStages], dDOk[kStages];
 #pragma unroll
       for (int i = 0; i < kStages; ++i) {
         const uint32_t q_s = ring + i * STAGE, do_s = q_s + Q_TILE;
         dQk[i] = umma_smem_desc(q_s, 0, 1024);
         dDOk[i] = umma_smem_desc(do_s, 0, 1024);
-        dQmn[i] = umma_smem_desc(q_s, Q_PANEL, 1024);
-        dDOmn[i] = umma_smem_desc(do_s, Q_PANEL, 1024);
       }
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        dP[i] = umma_smem_desc(p_s0 + i * 2 * P_TILE, 0, 1024);
-        dDS[i] = umma_smem_desc(p_s0 + i * 2 * P_TILE + P_TILE, 0, 1024);
-      }
-      auto issue_sdp = [&](int n) {
+      for (int n = 0; ok && n < nb; ++n) {
+        ok = mbar_wait(full0 + 8 * (n % kStages), (n / kStages) & 1, DEV_ERR_FULL_WAIT);
+        if (ok && n >= 2) ok = mbar_wait(sdp_free + 8 * (n & 1), ((n >> 1) - 1) & 1, DEV_ERR_EMPTY_WAIT);
+        if (!ok) break;
+        tc_fence_after();
         const uint64_t aq = (n % kStages) ? dQk[1] : dQk[0], ado = (n % kStages) ? dDOk[1] : dDOk[0];
         const uint32_t col = (n & 1) * 128;
-        // S and dP alternate: two MMAs in a row never accumulate into the same columns
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t aoff = (ks >> 2) * Q_PANEL + (ks & 3) * 32, boff = (ks >> 2) * KV_PANEL + (ks & 3) * 32;
@@ -253,15 +253,33 @@ __global__ void __launch_bounds__(kThreads, 1)
           umma_ss(tmem + col + 64, umma_desc_advance(ado, aoff), umma_desc_advance(dV, boff), idesc_kk, ks ? 1u : 0u);
         }
         umma_commit(sdp_full + 8 * (n & 1));
-      };
+      }
+    }
+  } else if (!skip && warp == kMma2Warp) {
+    // ------------------------------- MMA issuer B: dV, dK, dQ partials -----------------------------
+    if (lane == 0 && nb > 0) {
+      constexpr uint32_t idesc_mn = umma_idesc_bf16(128, 64, 1, 1);   // both operands MN-major
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, 0, 1);  // A = dS K-major, B = K MN-major
-      const uint64_t dKmn = umma_smem_desc(k_s, KV_PANEL, 1024);
-      uint64_t dDSk[2];
+      bool ok = mbar_wait(kv_bar, 0, DEV_ERR_FULL_WAIT);
+      uint64_t dQmn[kStages], dDOmn[kStages], dP[2], dDS[2], dDSk[2];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) dDSk[i] = umma_smem_desc(p_s0 + i * 2 * P_TILE + P_TILE, 0, 1024);
+      for (int i = 0; i < kStages; ++i) {
+        const uint32_t q_s = ring + i * STAGE, do_s = q_s + Q_TILE;
+        dQmn[i] = umma_smem_desc(q_s, Q_PANEL, 1024);
+        dDOmn[i] = umma_smem_desc(do_s, Q_PANEL, 1024);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        dP[i] = umma_smem_desc(p_s0 + i * 2 * P_TILE, 0, 1024);
+        dDS[i] = umma_smem_desc(p_s0 + i * 2 * P_TILE + P_TILE, 0, 1024);
+        dDSk[i] = dDS[i];   // the same tile read K-major for the dQ partial
+      }
+      const uint64_t dKmn = umma_smem_desc(k_s, KV_PANEL, 1024);
       int ndq = 0;          // dQ partials issued so far
-      int dq_pending = -1;  // batch whose dQ partial waits for the accumulator to be drained
-      auto issue_dkv = [&](int n) {
+      for (int n = 0; ok && n < nb; ++n) {
+        ok = mbar_wait(pds_full + 8 * (n & 1), (n >> 1) & 1, DEV_ERR_FULL_WAIT);
+        if (!ok) break;
+        tc_fence_after();
         const uint64_t aq = (n % kStages) ? dQmn[1] : dQmn[0], ado = (n % kStages) ? dDOmn[1] : dDOmn[0];
         const uint64_t bp = (n & 1) ? dP[1] : dP[0], bds = (n & 1) ? dDS[1] : dDS[0];
 #pragma unroll
@@ -270,59 +288,19 @@ __global__ void __launch_bounds__(kThreads, 1)
           umma_ss(tmem + kColDK, umma_desc_advance(aq, ks * 2048), umma_desc_advance(bds, ks * 2048), idesc_mn, (n | ks) ? 1u : 0u);
         }
         umma_commit(empty0 + 8 * (n % kStages));
-        if (emit_dq && (n % nb_sub) < nbA)
-          dq_pending = n;                  // its dS tile stays in use until the partial has been issued
-        else
-          umma_commit(pds_free + 8 * (n & 1));
-      };
-      auto issue_dq = [&](int n) {
-        const uint64_t ads = (n & 1) ? dDSk[1] : dDSk[0];
+        if (emit_dq && (n % nb_sub) < nbA) {
+          // the previous partial must have been read out of its accumulator by the drain warps
+          if (ndq > 0) ok = mbar_wait(dq_free, (ndq - 1) & 1, DEV_ERR_EMPTY_WAIT);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t ads = (n & 1) ? dDSk[1] : dDSk[0];
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)   // contraction over the 64 keys, 16 per step
-          umma_ss(tmem + kColDQ, umma_desc_advance(ads, ks * 32), umma_desc_advance(dKmn, ks * 2048), idesc_dq, ks ? 1u : 0u);
-        umma_commit(dq_full);
+          for (int ks = 0; ks < 4; ++ks)   // contraction over the 64 keys, 16 per step
+            umma_ss(tmem + kColDQ, umma_desc_advance(ads, ks * 32), umma_desc_advance(dKmn, ks * 2048), idesc_dq, ks ? 1u : 0u);
+          umma_commit(dq_full);
+          ++ndq;
+        }
         umma_commit(pds_free + 8 * (n & 1));
-        ++ndq;
-      };
-      // Event loop: dV/dK of batch `nd` is issued as soon as its P/dS tiles are written, S/dP of batch `ns` as soon as
-      // its Q/dO stage has landed and its TMEM buffer is free, the dQ partial of a selected batch as soon as the
-      // soft-max warps have read the previous partial out of its accumulator -- whichever becomes ready first.
-      // Waiting for them in a fixed order left the tensor core idle for a whole TMA latency per batch: the stage of
-      // batch n+2 is only freed by dV/dK of batch n, so a thread blocked on that stage could not issue dV/dK of
-      // batch n+1.
-      int ns = 0, nd = 0;
-      uint64_t t_idle = 0;
-      while (ok && (nd < nb || dq_pending >= 0)) {
-        bool progressed = false;
-        if (dq_pending >= 0 && (ndq == 0 || mbar_test(dq_free, (ndq - 1) & 1))) {
-          tc_fence_after();
-          issue_dq(dq_pending);
-          dq_pending = -1;
-          progressed = true;
-        }
-        if (ns < nb && ns < nd + 2 && mbar_test(full0 + 8 * (ns % kStages), (ns / kStages) & 1) &&
-            (ns < 2 || mbar_test(sdp_free + 8 * (ns & 1), ((ns >> 1) - 1) & 1))) {
-          tc_fence_after();
-          issue_sdp(ns);
-          ++ns;
-          progressed = true;
-        }
-        if (nd < ns && dq_pending < 0 && mbar_test(pds_full + 8 * (nd & 1), (nd >> 1) & 1)) {
-          tc_fence_after();
-          issue_dkv(nd);
-          ++nd;
-          progressed = true;
-        }
-        if (progressed) {
-          t_idle = 0;
-        } else {   // bounded: ~2 s without any progress is reported as a pipeline failure
-          const uint64_t now = global_timer_ns();
-          if (t_idle == 0) t_idle = now;
-          else if (now - t_idle > 2000000000ull) {
-            atomicCAS(&g_dev_error, 0, (int)DEV_ERR_FULL_WAIT);
-            ok = false;
-          }
-        }
       }
       umma_commit(acc_full);
     }
@@ -404,7 +382,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (!skip) {
     // ------------------------------- soft-max warps: one (token, head) row per thread --------------
     const int quad = warp & 3;
-    const int half = (warp - kMmaWarp - 1) >> 2; // which 32 key columns this thread owns
+    const int half = (warp - kSoftWarp) >> 2;    // which 32 key columns this thread owns
     const int row = 32 * quad + lane;           // TMEM lane == tile row
     const int j = row >> 4, head = row & 15;
     const uint32_t lane_addr = (uint32_t)(32 * quad) << 16;
