@@ -225,9 +225,10 @@ def per_kernel_breakdown(torch, nsa_b200, mod, q4, k4, v4, do4, reps=3):
         "sel_fwd": lambda: L.nsa_sel_swa_fwd(P(q4), P(k4), P(v4), P(idx), 0, None, P(o_slc), P(lse_slc), None, None, None,
                                              None, None, None, None, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"], 0,
                                              scale, S()),
-        # option, not in a module step: the same forward key-major on the tensor cores (reverse index, one CTA per key
-        # block over the queries that selected it, per-visit partial tiles, slot-order merge)
-        "sel_fwd_keymajor(option)": lambda: L.nsa_sel_swa_fwd_ws(
+        # what a module step runs: the same forward key-major on the tensor cores (reverse index, one CTA per key block
+        # over the queries that selected it, per-visit partial tiles, slot-order merge); "sel_fwd" above is the
+        # query-major kernel that runs without a workspace
+        "sel_fwd_keymajor(+reverse index,+merge)": lambda: L.nsa_sel_swa_fwd_ws(
             P(q4), P(k4), P(v4), P(idx), 0, None, P(o_slc), P(lse_slc), None, None, None, None, None, None, None, P(ws1),
             ws1.numel(), B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"], 0, scale, T, 0, S()),
         "gather_probe": lambda: L.nsa_gather_probe(P(k4), P(v4), P(idx), 0, B, T, Hq, Hkv, D, c["n_sel"], c["sel_block"],
@@ -468,7 +469,8 @@ def run_gpu(args):
         # algorithmic flops per kernel launch (per rank): forward 4D per (row,key); the backward's 10D per (row,key)
         # is split 4D to the dQ kernel (dQ + half of the S/dP recompute) and 6D to the dK/dV kernel
         kflops = {
-            "sel_fwd": fm_loc["slc"], "swa_fwd": fm_loc["swa"], "cmp_attn_fwd+select": fm_loc["cmp"],
+            "sel_fwd": fm_loc["slc"], "sel_fwd_keymajor(+reverse index,+merge)": fm_loc["slc"], "swa_fwd": fm_loc["swa"],
+            "cmp_attn_fwd+select": fm_loc["cmp"],
             "sel_dq": fm_loc["slc"], "swa_dq": fm_loc["swa"], "cmp_dq": fm_loc["cmp"],
             "sel+swa_dkv(+reverse index)": 1.5 * (fm_loc["slc"] + fm_loc["swa"]), "cmp_dkv(+reduce)": 1.5 * fm_loc["cmp"],
             # the whole 10D of the selected branch (S, dP, dV, dK, dQ) and the window's 6D in one pass over the keys
@@ -479,8 +481,8 @@ def run_gpu(args):
         # one ncu capture of the B=1 slice of this workload (`--profile-case`), in MB per sequence; traffic grows in
         # proportion to the number of sequences (every sequence's K/V stays in L2, q/dO/o/dq are streamed once).
         # NCU_TRAFFIC_COMMIT names the build the capture was taken from: a kernel changed since then has a stale entry.
-        # not part of the module's step with the large workspace: the query-major selected dQ and the dK/dV-only call
-        not_in_step = ("sel_dq", "sel+swa_dkv(+reverse index)")
+        # not part of the module's step with the workspaces: the query-major selected forward and dQ, the dK/dV-only call
+        not_in_step = ("sel_fwd", "sel_dq", "sel+swa_dkv(+reverse index)")
         dom = max((n for n in kern if n in kflops and n not in not_in_step), key=lambda n: kern[n])
         # kernels timed alone (three launches back to back): the burst bf16 peak is their denominator
         peak = peaks["tf_burst"]

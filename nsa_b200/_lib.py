@@ -99,7 +99,7 @@ def sel_swa_bwd_workspace_bytes(B, T, Tq, Hq, Hkv, D, S, BS):
 
 
 # Selected-branch forward key-major on the tensor cores (needs a workspace of about B*Tq*Hq*S*D*2 bytes) or query-major.
-SEL_FWD_KV = False
+SEL_FWD_KV = True
 
 
 def sel_swa_fwd_workspace_bytes(B, T, Tq, Hq, Hkv, D, S, BS):

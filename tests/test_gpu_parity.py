@@ -166,12 +166,12 @@ def test_selection_bwd_query_major_dq(nsa, case):
 
 
 @pytest.mark.parametrize("case", [(128, 64, 4, 32, 2, 384, 100), (128, 64, 20, 16, 1, 450, 0), (128, 64, 4, 32, 1, 300, 64)])
-def test_selection_fwd_key_major(nsa, case):
-    """The same comparison with the selected branch's forward run key-major on the tensor cores (reverse index, per-visit
-    partial tiles, slot-order merge): an option of nsa_sel_swa_fwd_ws, off by default because it is not faster.  The
-    last case has two 16-head groups per KV head."""
+def test_selection_fwd_query_major(nsa, case):
+    """The same comparison with the selected branch's forward on the query-major kernel (no workspace) instead of the
+    key-major tensor-core path (reverse index, per-visit partial tiles, slot-order merge), which is the default and which
+    the test above covers.  The last case has two 16-head groups per KV head."""
     old = nsa._lib.SEL_FWD_KV
-    nsa._lib.SEL_FWD_KV = True
+    nsa._lib.SEL_FWD_KV = False
     try:
         test_selection_and_window_fwd_bwd(nsa, *case)
     finally:
