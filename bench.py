@@ -37,11 +37,13 @@ CFG = dict(B=8, T=8192, Hq=64, Hkv=4, D=128, block=32, stride=16, sel_block=64, 
 WORKLOAD = "configs[2]: NSAAttention module fwd+bwd bf16, B=8 T=8192 Hq=64 Hkv=4 D=128, cmp 32/16, sel 64 top-16, window 512"
 METRIC = "NSA fwd+bwd tokens/s"
 # ncu DRAM traffic per launch, MB per 8192-token sequence (see run_gpu), and the build it was captured from
-NCU_TRAFFIC_COMMIT = "ff75ab1"
-NCU_MB_PER_SEQ = {"sel_fwd": 238, "sel_dq": 377, "sel+swa_dkv(+reverse index)": 890, "cmp_attn_fwd+select": 226,
-                  "swa_fwd": 243, "swa_dq": 395, "cmp_dq": 375, "cmp_dkv(+reduce)": 287,
-                  # key-major kernel with dQ partials 1290 read + 1080 written, their reduction 1210 + 83
-                  "sel+swa_dkv+sel_dq(+reverse index,+reduce)": 3663}
+NCU_TRAFFIC_COMMIT = "37145d8"
+NCU_MB_PER_SEQ = {"sel_fwd": 238, "sel_dq": 376, "sel+swa_dkv(+reverse index)": 867, "cmp_attn_fwd+select": 227,
+                  "swa_fwd": 243, "swa_dq": 394, "cmp_dq": 375, "cmp_dkv(+reduce)": 277,
+                  # key-major forward 201 read + 1046 written, its merge 1109 + 89
+                  "sel_fwd_keymajor(+reverse index,+merge)": 2445,
+                  # key-major kernel with dQ partials 1268 read + 1077 written, their reduction 1210 + 82
+                  "sel+swa_dkv+sel_dq(+reverse index,+reduce)": 3637}
 
 
 # ---------------------------------------------------------------------------------------------------------
