@@ -357,16 +357,29 @@ __global__ void __launch_bounds__(256) sel_fwd_merge_kernel(const RevArgs a, con
     const long long pos = __shfl_sync(0xffffffffu, mypos, s);
     return (bh * a.cap + pos) * G16 + sub;
   };
-  // pass 1: lanes 0-7 = heads hb*8 + lane: M = max_v m_v, L = sum_v 2^(m_v - M) l_v
+  // pass 1: M = max_v m_v per head.  Lane s fetches the maxima of slot s for this half's eight heads (all slots at
+  // once, instead of one dependent load per slot), a butterfly takes the maximum over the slots, and every lane keeps
+  // the value of head lane & 7, the head whose (m, l) it reads in pass 2.
   const int myhead = hb * 8 + (lane & 7);
-  float M = -INFINITY;
-  for (unsigned rem = live; rem;) {
-    const int s = __ffs(rem) - 1;
-    rem &= rem - 1;
-    const long long ti = tile_index(s);
-    const float2 ml = reinterpret_cast<const float2*>(stats)[ti * 16 + myhead];
-    M = fmaxf(M, ml.x);
+  float mh[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) mh[e] = -INFINITY;
+  if (mypos >= 0) {
+    const float4* sp = reinterpret_cast<const float4*>(stats) + (((bh * a.cap + mypos) * G16 + sub) * 16 + hb * 8) / 2;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float4 v4 = sp[e];   // (m, l) of two heads
+      mh[2 * e] = v4.x;
+      mh[2 * e + 1] = v4.z;
+    }
   }
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mh[e] = fmaxf(mh[e], __shfl_xor_sync(0xffffffffu, mh[e], off));
+  float M = mh[0];
+#pragma unroll
+  for (int e = 1; e < 8; ++e) M = ((lane & 7) == e) ? mh[e] : M;
   float L = 0.f;
   float acc[NV][8];
 #pragma unroll
