@@ -248,7 +248,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         // memory at about 20 bytes per cycle, which made this read-out the kernel's bottleneck
         bool good = mbar_wait(stg_full, n & 1, DEV_ERR_FULL_WAIT);
         const int nvalid = min(kTokB, nA - mloc * kTokB);
-        if (good && lane < nvalid) {
+        if (good && G16 == 1 && lane == 0 && nvalid > 0) {
+          bf16* dst = a.part + (((long long)bh * a.rev_cap + ta_lo + mloc * kTokB) * (16 * D));
+          bulk_store_evict_first(dst, sb, (uint32_t)nvalid * 16 * D * 2);
+        } else if (good && G16 > 1 && lane < nvalid) {
           bf16* dst = a.part + ((((long long)bh * a.rev_cap + ta_lo + mloc * kTokB + lane) * G16 + sub) * (16 * D));
           bulk_store_evict_first(dst, sb + lane * 16 * D * 2, 16 * D * 2);
         }
