@@ -37,13 +37,13 @@ CFG = dict(B=8, T=8192, Hq=64, Hkv=4, D=128, block=32, stride=16, sel_block=64, 
 WORKLOAD = "configs[2]: NSAAttention module fwd+bwd bf16, B=8 T=8192 Hq=64 Hkv=4 D=128, cmp 32/16, sel 64 top-16, window 512"
 METRIC = "NSA fwd+bwd tokens/s"
 # ncu DRAM traffic per launch, MB per 8192-token sequence (see run_gpu), and the build it was captured from
-NCU_TRAFFIC_COMMIT = "37145d8"
+NCU_TRAFFIC_COMMIT = "2bd6f3b"
 NCU_MB_PER_SEQ = {"sel_fwd": 238, "sel_dq": 376, "sel+swa_dkv(+reverse index)": 867, "cmp_attn_fwd+select": 227,
                   "swa_fwd": 243, "swa_dq": 394, "cmp_dq": 375, "cmp_dkv(+reduce)": 277,
-                  # key-major forward 201 read + 1046 written, its merge 1109 + 89
-                  "sel_fwd_keymajor(+reverse index,+merge)": 2445,
-                  # key-major kernel with dQ partials 1268 read + 1077 written, their reduction 1210 + 82
-                  "sel+swa_dkv+sel_dq(+reverse index,+reduce)": 3637}
+                  # key-major forward 203 read + 1046 written, its merge 1109 + 88
+                  "sel_fwd_keymajor(+reverse index,+merge)": 2446,
+                  # key-major kernel with dQ partials 1278 read + 1077 written, their reduction 1210 + 81
+                  "sel+swa_dkv+sel_dq(+reverse index,+reduce)": 3646}
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -601,6 +601,13 @@ def selection_microbench(torch, dev, peaks):
         _lib.check(L.nsa_sel_swa_fwd(P(q), P(k), P(v), P(idx), 0, None, P(o), P(lse), None, None, None, None, None, None,
                                      None, B, T, Hq, Hkv, D, n, BS, 0, scale, S()), "nsa_sel_swa_fwd")
 
+    nws = L.nsa_sel_swa_fwd_workspace_bytes(B, T, T, Hq, Hkv, D, n, BS)
+    ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+
+    def fwd_kv():   # the same forward key-major on the tensor cores (what the Python layer calls)
+        _lib.check(L.nsa_sel_swa_fwd_ws(P(q), P(k), P(v), P(idx), 0, None, P(o), P(lse), None, None, None, None, None, None,
+                                        None, P(ws), nws, B, T, Hq, Hkv, D, n, BS, 0, scale, T, 0, S()), "nsa_sel_swa_fwd_ws")
+
     def probe():
         _lib.check(L.nsa_gather_probe(P(k), P(v), P(idx), 0, B, T, Hq, Hkv, D, n, BS, S()), "nsa_gather_probe")
 
@@ -619,8 +626,10 @@ def selection_microbench(torch, dev, peaks):
 
     for _ in range(3):
         fwd()
+        fwd_kv()
         probe()
     torch.cuda.synchronize()
+    ms_kv, ms_kv_cold = timed(fwd_kv, 10, False), timed(fwd_kv, 5, True)
     ms_warm, ms_cold = timed(fwd, 10, False), timed(fwd, 5, True)
     ms_probe = timed(probe, 5, False)
     _lib.device_status()
@@ -631,6 +640,11 @@ def selection_microbench(torch, dev, peaks):
                         "indices uniform over causally valid blocks incl. block 0 and the local block, window 0, seed 1",
             "ms_warm_l2": round(ms_warm, 3), "ms_l2_flushed": round(ms_cold, 3),
             "tokens_per_s": B * T / (ms_warm * 1e-3),
+            "kernel": "query-major mma.sync kernel (nsa_sel_swa_fwd); the key-major tcgen05 path is beside it",
+            "key_major": {"entry": "nsa_sel_swa_fwd_ws (reverse index + tcgen05 key-major kernel + merge)",
+                          "ms_warm_l2": round(ms_kv, 3), "ms_l2_flushed": round(ms_kv_cold, 3),
+                          "tokens_per_s": B * T / (ms_kv * 1e-3), "tflops": round(flops / (ms_kv * 1e-3) / 1e12, 1),
+                          "workspace_bytes": int(nws)},
             "visited_blocks_per_token_kvhead": visits / (B * T * Hkv),
             "tflops": round(flops / (ms_warm * 1e-3) / 1e12, 1),
             "frac_of_burst_peak": round(flops / (ms_warm * 1e-3) / 1e12 / peaks["tf_burst"], 4),
