@@ -521,12 +521,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 // Merge of the per-warp partials: one CTA of D threads per (sequence, kv head); thread d owns channel d of the 16 rows.
 // Branch order in the workspace: 0 compressed, 1 selected, 2 window.  Fixed summation order (warp 0, 1, ...).  The gates
 // are computed here from q when the gate projection is given.
-__global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeArgs a) {
+// 4 x D threads per item: four groups of four query rows, one thread per output channel; the sums over the six
+// consumer warps are short, so the kernel is pure latency and the rows are spread over as many threads as the GPU holds.
+constexpr int kMergeGroups = 4;
+__global__ void __launch_bounds__(kMergeGroups * D) decode_merge_kernel(const DecodeArgs a) {
   const int item = blockIdx.x;
   const int sq = item / a.Hkv, h = item % a.Hkv;
   const int seq = a.order ? a.order[sq] : sq;
   const long long qrow = (long long)seq * a.Hq + h * 16;
-  const int d = threadIdx.x;
+  const int d = threadIdx.x & (D - 1);
+  const int rg = threadIdx.x / D;            // rows 4 rg .. 4 rg + 3
+  const int tid = threadIdx.x;
   const float* part = a.part + (long long)item * 3 * kCons * kPartFloats;
   __shared__ float w_s[3][kCons][16];   // per (branch, warp, row): 2^(m_w - M) / L
   __shared__ float lse_s[3][16];
@@ -536,9 +541,13 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeArgs a) {
     // g_x[row] = q[row,:] . W[x,:] + b[x] (nn.Linear(head_dim, 3), rows of W: selected, window, compressed), rounded to
     // bf16 as the module's gate tensors are
     const float w0 = __bfloat162float(a.gate_w[d]), w1 = __bfloat162float(a.gate_w[D + d]), w2 = __bfloat162float(a.gate_w[2 * D + d]);
-    for (int r = 0; r < 16; ++r) {
-      const float qv = __bfloat162float(a.q[(qrow + r) * D + d]);
-      float p0 = qv * w0, p1 = qv * w1, p2 = qv * w2;
+    float qa[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qa[i] = __bfloat162float(a.q[(qrow + rg * 4 + i) * D + d]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = rg * 4 + i;
+      float p0 = qa[i] * w0, p1 = qa[i] * w1, p2 = qa[i] * w2;
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) {
         p0 += __shfl_xor_sync(0xffffffffu, p0, off);
@@ -552,25 +561,32 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeArgs a) {
       }
     }
   }
-  if (d < 48) {
-    const int br = d / 16, r = d % 16;
+  // Launched with programmatic stream serialization: everything above (the gate projection reads only q and the
+  // weights) may run while the main kernel is still finishing; its partials are read only behind this wait.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (tid < 48) {
+    const int br = tid / 16, r = tid % 16;
     const float* base = part + (long long)br * kCons * kPartFloats;
+    float mw[kCons], lw[kCons];
+#pragma unroll
+    for (int w = 0; w < kCons; ++w) {
+      mw[w] = base[w * kPartFloats + 16 * D + r];
+      lw[w] = base[w * kPartFloats + 16 * D + 16 + r];
+    }
     float M = -INFINITY;
-    for (int w = 0; w < kCons; ++w) M = fmaxf(M, base[w * kPartFloats + 16 * D + r]);
+#pragma unroll
+    for (int w = 0; w < kCons; ++w) M = fmaxf(M, mw[w]);
     float Ltot = 0.f;
-    for (int w = 0; w < kCons; ++w) {
-      const float mw = base[w * kPartFloats + 16 * D + r];
-      if (mw > -INFINITY) Ltot += base[w * kPartFloats + 16 * D + 16 + r] * ex2(mw - M);
-    }
-    for (int w = 0; w < kCons; ++w) {
-      const float mw = base[w * kPartFloats + 16 * D + r];
-      w_s[br][w][r] = (mw > -INFINITY && Ltot > 0.f) ? ex2(mw - M) / Ltot : 0.f;
-    }
+#pragma unroll
+    for (int w = 0; w < kCons; ++w)
+      if (mw[w] > -INFINITY) Ltot += lw[w] * ex2(mw[w] - M);
+#pragma unroll
+    for (int w = 0; w < kCons; ++w) w_s[br][w][r] = (mw[w] > -INFINITY && Ltot > 0.f) ? ex2(mw[w] - M) / Ltot : 0.f;
     lse_s[br][r] = Ltot > 0.f ? (M + log2f(Ltot)) * kLn2 : -INFINITY;
   }
   __syncthreads();
-  if (d < 48) {
-    const int br = d / 16, r = d % 16;
+  if (tid < 48) {
+    const int br = tid / 16, r = tid % 16;
     const bf16* gin[3] = {a.g_cmp, a.g_slc, a.g_swa};
     float gv = 1.f;
     if (a.gate_w) {
@@ -586,7 +602,9 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeArgs a) {
   }
   __syncthreads();
   bf16* outs[3] = {a.o_cmp, a.o_slc, a.o_swa};
-  for (int r = 0; r < 16; ++r) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {   // this group's four rows: 72 independent loads in flight per thread
+    const int r = rg * 4 + i;
     float tot = 0.f;
 #pragma unroll
     for (int br = 0; br < 3; ++br) {
@@ -601,8 +619,8 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const DecodeArgs a) {
     }
     a.o[(qrow + r) * D + d] = __float2bfloat16(tot);
   }
-  if (a.lse && d < 48) {
-    const int br = d / 16, r = d % 16;
+  if (a.lse && tid < 48) {
+    const int br = tid / 16, r = tid % 16;
     if (!(br == 2 && a.window <= 0)) a.lse[(long long)br * a.nseq * a.Hq + qrow + r] = lse_s[br][r];
   }
 }
@@ -651,7 +669,23 @@ int launch_decode(const DecodeArgs& a, cudaStream_t s) {
   const int grid = nitem < num_sms() ? nitem : num_sms();
   if (grid <= 0) return 0;
   decode_kernel<<<grid, kThreads, smem, s>>>(tmK, tmV, tmCK, tmCV, a);
-  decode_merge_kernel<<<nitem, D, 0, s>>>(a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  {
+    // the merge kernel may be scheduled before the main kernel has drained (it waits with griddepcontrol.wait)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)nitem);
+    cfg.blockDim = dim3(kMergeGroups * D);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, decode_merge_kernel, a);
+    if (e != cudaSuccess) return (int)e;
+  }
   note_launches(2);
   return (int)cudaGetLastError();
 }
