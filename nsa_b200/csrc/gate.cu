@@ -152,6 +152,43 @@ __global__ void __launch_bounds__(kGateThreads) rowdot3_kernel(const Rowdot3Args
   }
 }
 
+// The same pre-pass with one row per group of D/8 lanes and one block per 256 / (D/8) rows (no grid-stride loop): few
+// registers, so many small blocks are resident and the memory system sees the access pattern of the combine kernel.
+// Measured against the persistent form above at 4.2 M rows: 0.69 against 1.05 ms (6.25 against 4.1 TB/s).
+template <int D>
+__global__ void __launch_bounds__(256) rowdot3_flat_kernel(const Rowdot3Args a) {
+  constexpr int LPR = D / 8;
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long row = i / LPR;
+  const int sub = (int)(i % LPR);
+  const bool live = row < a.rows;
+  uint4 draw = make_uint4(0u, 0u, 0u, 0u), vraw[3];
+  float gv[3] = {1.f, 1.f, 1.f};
+  if (live) draw = ldraw(a.dout + row * D + sub * 8);
+#pragma unroll
+  for (int x = 0; x < 3; ++x) {
+    vraw[x] = make_uint4(0u, 0u, 0u, 0u);
+    if (live && a.o[x]) vraw[x] = ldraw(a.o[x] + row * D + sub * 8);
+    if (live && sub == 0 && a.o[x] && a.gate[x]) gv[x] = __bfloat162float(a.gate[x][row]);
+  }
+  float du[8];
+  cvt8(draw, du);
+#pragma unroll
+  for (int x = 0; x < 3; ++x) {
+    if (!a.o[x]) continue;   // uniform
+    float vu[8];
+    cvt8(vraw[x], vu);
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += vu[k] * du[k];
+    s = group_sum<LPR>(s);
+    if (live && sub == 0) {
+      if (a.delta[x]) a.delta[x][row] = s * gv[x];
+      if (a.dgate[x]) a.dgate[x][row] = __float2bfloat16(s);
+    }
+  }
+}
+
 // dq[row] += sum_g dg_g[row] * W[g];  per-block partials of dW[g] = sum_rows dg_g[row] * q[row] and db[g] = sum_rows dg_g
 template <int D>
 __global__ void __launch_bounds__(kGateThreads, 2) gate_bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ dg0,
@@ -288,7 +325,7 @@ int launch_rowdot3(const bf16* const o[3], const bf16* dout, const bf16* const g
   a.dout = dout;
   a.rows = rows;
   if (D == 128)
-    rowdot3_kernel<128><<<stream_grid(rowdot3_kernel<128>, rows, 16), kGateThreads, 0, s>>>(a);
+    rowdot3_flat_kernel<128><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, s>>>(a);
   else if (D == 64)
     rowdot3_kernel<64><<<stream_grid(rowdot3_kernel<64>, rows, 32), kGateThreads, 0, s>>>(a);
   else {
