@@ -178,6 +178,50 @@ def test_selection_fwd_query_major(nsa, case):
         nsa._lib.SEL_FWD_KV = old
 
 
+def test_workspace_size_selects_the_selected_branch_kernels(nsa):
+    """The C entry points pick the key-major tensor-core kernels only when the caller's workspace is large enough:
+    a workspace that is too small must give exactly the query-major results (forward), and the two backward forms
+    must agree (dK, dV bit-equal: the same kernel with and without the dQ partials; dQ within the bf16 rounding of
+    the partial tiles)."""
+    L, P, S = nsa._lib.lib(), nsa._lib.ptr, nsa._lib.stream
+    B, T, Hq, Hkv, D, n, BS = 1, 640, 32, 2, 128, 6, 64
+    gen = torch.Generator().manual_seed(77)
+    q, do = (_dev(_r(torch.randn(B, T, Hq, D, generator=gen))) for _ in range(2))
+    k, v = (_dev(_r(torch.randn(B, T, Hkv, D, generator=gen))) for _ in range(2))
+    idx = _rand_indices(B, T, Hkv, n, BS, gen).to(torch.int32).to(DEV).contiguous()
+    scale = D ** -0.5
+    outs = []
+    nws = L.nsa_sel_swa_fwd_workspace_bytes(B, T, T, Hq, Hkv, D, n, BS)
+    for ws_bytes in (0, 4096, nws):
+        o = torch.empty_like(q)
+        lse = torch.empty(B, T, Hq, dtype=torch.float32, device=DEV)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=DEV)
+        nsa._lib.check(L.nsa_sel_swa_fwd_ws(P(q), P(k), P(v), P(idx), 0, None, P(o), P(lse), None, None, None, None, None,
+                                            None, None, P(ws) if ws_bytes else None, ws_bytes, B, T, Hq, Hkv, D, n, BS, 0,
+                                            scale, T, 0, S()), "nsa_sel_swa_fwd_ws")
+        outs.append((o, lse))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    _close("o key-major vs query-major", outs[2][0], outs[0][0].float().cpu())
+    fin = torch.isfinite(outs[0][1])
+    assert torch.equal(fin, torch.isfinite(outs[2][1]))
+    assert (outs[2][1][fin] - outs[0][1][fin]).abs().max().item() < 5e-3
+    o, lse = outs[0]
+    delta = (o.float() * do.float()).sum(-1).contiguous()
+    res = []
+    for big in (False, True):
+        nb = (L.nsa_sel_swa_bwd_workspace_bytes_dq(B, T, T, Hq, Hkv, D, n, BS) if big
+              else L.nsa_sel_swa_bwd_workspace_bytes(B, T, Hkv, n, BS))
+        ws = torch.empty(nb, dtype=torch.uint8, device=DEV)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        nsa._lib.check(L.nsa_sel_swa_bwd(P(q), P(k), P(v), P(idx), 0, None, P(do), P(lse), P(delta), None, None, None, None,
+                                         None, P(dq), 0, P(dk), P(dv), P(ws), nb, B, T, Hq, Hkv, D, n, BS, 0, scale, S()),
+                       "nsa_sel_swa_bwd")
+        res.append((dq, dk, dv))
+    assert torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][2], res[1][2])
+    _close("dq key-major vs query-major", res[1][0], res[0][0].float().cpu())
+    nsa._lib.device_status()
+
+
 def test_selection_varlen_cu_seqlens(nsa):
     """parallel_nsa with cu_seqlens (packed sequences of different lengths, batch 1): block indices and masks are
     relative to each sequence, as in the reference's varlen indexing (nsa/selection_attn.py:419-425).  Forward and
