@@ -230,6 +230,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   } else {
     // ------------------------------- soft-max warps ------------------------------------------------
+    // budget: the CTA is launched with 384 x 168 = 64512 registers; 128 x 72 + 256 x 216 = 64512 (an inc that the launch
+    // pool cannot satisfy blocks for ever)
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int quad = warp & 3;
     const int half = (warp - 4) >> 2;

@@ -164,6 +164,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   // 512 threads start with 128 registers each; the soft-max warps need 168.  Warps 0-3 (TMA, MMA) and 12-15 (drain)
   // give registers back, warps 4-11 take them (each instruction is executed by a whole warpgroup).
   // Each role's code follows its own setmaxnreg, so the compiler allocates registers for it under that budget.
+  // Budget (setmaxnreg moves registers inside the pool the CTA was launched with, 512 x 128 = 65536; an inc that the
+  // pool cannot satisfy blocks for ever): 128 x 80 + 256 x 168 + 128 x 88 = 64512.
   if (warp < 4) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
   if (!skip && warp < kProd) {
