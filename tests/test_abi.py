@@ -39,7 +39,19 @@ def test_argument_checks_need_no_gpu():
     assert rc == -3 and b"multiple of 16" in L.nsa_last_error()
     rc = L.nsa_cmp_attn_fwd(one, one, one, one, one, None, None, 1, 64, 3, 16, 1, 96, 32, 16, 1, 1.0, 0, 0, 0, 0, None)
     assert rc == -2 and b"head_dim" in L.nsa_last_error()
-    assert L.nsa_sel_swa_bwd_workspace_bytes(8, 8192, 4, 16, 64) > 8 * 4 * 8192 * 16 * 4
+    base = L.nsa_sel_swa_bwd_workspace_bytes(8, 8192, 4, 16, 64)
+    assert base > 8 * 4 * 8192 * 16 * 4
+    # the larger workspaces add one [16 heads x D] bf16 tile per (token, kv head, slot): B*T*Hq*S*D*2 bytes, plus the
+    # inverse index (and, for the forward, 16 (max, sum) pairs per tile)
+    tiles = 8 * 8192 * 64 * 16 * 128 * 2
+    dq = L.nsa_sel_swa_bwd_workspace_bytes_dq(8, 8192, 8192, 64, 4, 128, 16, 64)
+    fw = L.nsa_sel_swa_fwd_workspace_bytes(8, 8192, 8192, 64, 4, 128, 16, 64)
+    assert base + tiles < dq < base + tiles + (1 << 28) and dq < fw < dq + (1 << 30)
+    # a query shard needs tiles for its own rows only
+    assert L.nsa_sel_swa_fwd_workspace_bytes(1, 65536, 8192, 64, 4, 128, 16, 64) < fw
+    from nsa_b200 import _lib as lib_mod
+    assert lib_mod.sel_swa_fwd_workspace_bytes(1, 512, 512, 16, 1, 64, 4, 64) == 0      # head_dim 64: query-major kernel
+    assert lib_mod.sel_swa_fwd_workspace_bytes(1, 512, 512, 16, 1, 128, 4, 32) == 0     # 32-key blocks: query-major kernel
     assert L.nsa_kernel_launch_count() == 0
 
 
